@@ -44,6 +44,7 @@ class Options(C.Structure):
 QUANT_NONE, QUANT_INT8, QUANT_NF4 = 0, 1, 2
 ARCH_KEMIRAX = 100          # Info.version of the config.json-described families
 ARCH_DEGAVIK = 101
+ARCH_ZUFULIX = 102
 
 
 class B200Error(RuntimeError):

@@ -1,0 +1,274 @@
+// Causal softmax attention over a paged key / value cache with a learned bias per (distance, head) and no rotation: positions
+// enter only through the bias.
+//
+// H query heads, G key / value heads (query head h reads head h / (H / G)).  Per layer and token the cache row holds the G keys
+// (unit root-mean-square) followed by the G values: D = G (dk + dv) floats.  For query position i and key position j <= i
+//     s_h(i, j) = (q_h(i) . k(j)) * scale + bias[min(i - j, nb)][h]
+//     o_h(i) = sum_j softmax_j(s_h(i, .)) v(j)
+// The table bias[0 .. nb][H] is built by the host from the model's bucket table (distances share buckets that are evenly
+// spaced in the logarithm of the distance; everything from nb on shares the last one), so the kernel knows nothing of buckets
+// and another bias law is another table.
+// The values may be blended with those another layer computed for the same token before they are cached:
+//     v <- (1 - lam) v + lam v_first
+//
+//   bias_attn_prep_kernel   per token: q heads / rms(q) * scale -> q buffer;  k heads / rms(k) and the (blended) v -> the cache
+//                           row of (slot, position); the first blending layer also leaves its v in the step's v_first buffer.
+//   bias_attn_kernel        a cluster of 1..8 CTAs per chunk of consecutive tokens of one sequence (SeqMeta chunks), all heads;
+//                           the 32-key tiles up to the chunk's last position are dealt out among the cluster's CTAs; every CTA
+//                           walks its tiles ONCE with a running maximum / sum per (token, head) row (online softmax) and the
+//                           CTAs' partial results are merged through distributed shared memory in rank order.  A warp owns
+//                           four rows of one key / value head: it scores them against a key per lane, then applies the tile's
+//                           weights to the values, with no CTA barrier in between.  Scores, weights and sums in f32.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include "common.cuh"
+#include "latent_attn.cuh"
+#include "linear.cuh"
+
+namespace b200 {
+
+enum BiasAttnVMode { BA_V_PLAIN = 0, BA_V_FIRST = 1, BA_V_BLEND = 2 };
+
+struct BiasAttnPrepParams {
+    const float* q; const float* k; const float* v; int ld;      // projection rows: q [H * dk], k [G * dk], v [G * dv]
+    float* qo; int ldq;                           // [T, H * dk]
+    float* cache;                                 // [pages][page][G * dk + G * dv]
+    const int* table; int stride; int page;
+    float* vfirst; int ldv;                       // [T, G * dv] values of the first blending layer (this step's tokens)
+    int vmode; float lam;
+    int H, G, dk, dv;
+    float scale, eps;
+    MetaView meta; SeqMeta sm;
+};
+
+__global__ void __launch_bounds__(128) bias_attn_prep_kernel(const BiasAttnPrepParams p) {
+    const int t = blockIdx.x;
+    if (t >= p.meta.T()) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int slot = p.meta.tok_slot()[t], ipos = p.sm.tok_pos()[t];
+    const int D = p.G * (p.dk + p.dv);
+    float* row = p.cache + ((size_t)p.table[(size_t)slot * p.stride + ipos / p.page] * p.page + ipos % p.page) * D;
+    for (int hh = warp; hh < p.H + p.G; hh += nw) {
+        const bool isq = hh < p.H;
+        const int h = isq ? hh : hh - p.H;
+        const float* src = (isq ? p.q : p.k) + (size_t)t * p.ld + (size_t)h * p.dk;
+        float* dst = isq ? p.qo + (size_t)t * p.ldq + (size_t)h * p.dk : row + (size_t)h * p.dk;
+        float ss = 0.f;
+        for (int i = lane; i < p.dk; i += 32) ss = fmaf(src[i], src[i], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float r = (isq ? p.scale : 1.f) / sqrtf(ss / (float)p.dk + p.eps);
+        for (int i = lane; i < p.dk; i += 32) dst[i] = src[i] * r;
+    }
+    float* vdst = row + (size_t)p.G * p.dk;
+    const float* vsrc = p.v + (size_t)t * p.ld;
+    float* vf = p.vfirst + (size_t)t * p.ldv;
+    for (int i = threadIdx.x; i < p.G * p.dv; i += blockDim.x) {
+        float val = vsrc[i];
+        if (p.vmode == BA_V_FIRST) vf[i] = val;
+        else if (p.vmode == BA_V_BLEND) val = (1.f - p.lam) * val + p.lam * vf[i];
+        vdst[i] = val;
+    }
+}
+
+struct BiasAttnParams {
+    const float* q; int ldq;                      // [T, H * dk] prepared queries
+    const float* cache;
+    const int* table; int stride; int page;
+    float* out; int ldo;                          // [T, H * dv]
+    const float* bias; int nb;                    // [nb + 1][H]
+    int H, G, dk, dv;
+    int qb;                                       // tokens per chunk the shared memory was sized for
+    int gt;                                       // key / value heads per tile load
+    int cl;                                       // CTAs per chunk (cluster size)
+    MetaView meta; SeqMeta sm;
+};
+
+constexpr int BA_KT = 32;                          // keys per tile (one per lane in the score phase)
+constexpr int BA_THREADS = 512;                    // most threads per CTA; the host launches 256 where fewer warps find work
+constexpr int BA_RB = 4;                           // rows of one key / value head a warp works on together
+
+__host__ __device__ inline size_t bias_attn_smem(int qb, int H, int dk, int dv, int gt) {
+    const size_t R = (size_t)qb * H;
+    return (R * dk + R * dv + R * BA_KT + (size_t)gt * BA_KT * (dk + 4 + dv + 4) + 3 * R + 8) * sizeof(float);
+}
+
+// `nk` cache rows from position j0 on: `wk` floats at offset `offk` and `wv` floats at offset `offv` of each of `gn` consecutive
+// heads -> tk[head][key][tsk], tv[head][key][tsv]; value rows past nk are zero (their weights are zero too, and 0 * junk must
+// stay 0).  vec: 16-byte cp.async copies, a warp per cache row, all copies of the tile in flight together.
+__device__ __forceinline__ void ba_load_tiles(const float* cache, const int* tbl, int page, int D, size_t offk, int wk, size_t offv, int wv,
+                                              float* tk, int tsk, float* tv, int tsv, int gn, int nk, int j0, bool vec) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (int)(blockDim.x >> 5);
+    for (int kt = warp; kt < BA_KT; kt += nw) {
+        if (kt >= nk) {
+            for (int c = 0; c < gn; ++c)
+                for (int i = lane; i < wv; i += 32) tv[((size_t)c * BA_KT + kt) * tsv + i] = 0.f;
+            continue;
+        }
+        const int j = j0 + kt, pg = j / page;
+        const float* src = cache + ((size_t)tbl[pg] * page + (j - pg * page)) * D;
+        if (vec) {
+            for (int c = 0; c < gn; ++c) {
+                for (int v4 = lane; v4 < (wk >> 2); v4 += 32) cp_async16(tk + ((size_t)c * BA_KT + kt) * tsk + v4 * 4, src + offk + (size_t)c * wk + v4 * 4);
+                for (int v4 = lane; v4 < (wv >> 2); v4 += 32) cp_async16(tv + ((size_t)c * BA_KT + kt) * tsv + v4 * 4, src + offv + (size_t)c * wv + v4 * 4);
+            }
+        } else {
+            for (int c = 0; c < gn; ++c) {
+                for (int i = lane; i < wk; i += 32) tk[((size_t)c * BA_KT + kt) * tsk + i] = src[offk + (size_t)c * wk + i];
+                for (int i = lane; i < wv; i += 32) tv[((size_t)c * BA_KT + kt) * tsv + i] = src[offv + (size_t)c * wv + i];
+            }
+        }
+    }
+    if (vec) {
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnParams p) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = p.cl, rank = blockIdx.x % CL, ch = blockIdx.x / CL;
+    if (ch >= p.sm.n_chunks()) return;             // the same for every CTA of a cluster
+    const int t0 = p.sm.chunk_start()[ch], nq = p.sm.chunk_count()[ch];
+    const int slot = p.meta.tok_slot()[t0];
+    const int pos0 = p.sm.tok_pos()[t0], pos1 = pos0 + nq - 1;
+    const int H = p.H, G = p.G, dk = p.dk, dv = p.dv, rep = H / G, R = nq * H;
+    // head sizes that are multiples of four: tile rows start on 16 bytes (stride d + 4: a quarter warp's 16-byte reads of eight
+    // different rows fall into different banks) and arrive by cp.async; otherwise stride d + 1 and scalar loads
+    const bool vec = (dk % 4 == 0) && (dv % 4 == 0);
+    const int tsk = dk + (vec ? 4 : 1), tsv = dv + (vec ? 4 : 1), D = G * (dk + dv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    extern __shared__ __align__(16) float ba_smem[];
+    const int Rcap = p.qb * H;
+    float* sP = ba_smem;                           // [R][KT] weights of the tile (rows start on 16 bytes for any head size)
+    float* sK = sP + (size_t)Rcap * BA_KT;         // [gt][KT][tsk]
+    float* sV = sK + (size_t)p.gt * BA_KT * (dk + 4);   // [gt][KT][tsv]
+    float* sQ = sV + (size_t)p.gt * BA_KT * (dv + 4);   // [R][dk]
+    float* sO = sQ + (size_t)Rcap * dk;            // [R][dv] un-normalised outputs
+    float* sMax = sO + (size_t)Rcap * dv;          // [R] running maximum / sum / last rescale of this CTA
+    float* sSum = sMax + Rcap;
+    float* sScl = sSum + Rcap;
+    for (int e = threadIdx.x; e < R * dk; e += (int)blockDim.x) {
+        const int r = e / dk, i = e % dk;
+        sQ[e] = p.q[(size_t)(t0 + r / H) * p.ldq + (size_t)(r % H) * dk + i];
+    }
+    for (int e = threadIdx.x; e < R * dv; e += (int)blockDim.x) sO[e] = 0.f;
+    for (int e = threadIdx.x; e < R; e += (int)blockDim.x) { sMax[e] = -CUDART_INF_F; sSum[e] = 0.f; sScl[e] = 1.f; }
+    const int ntiles = (pos1 + BA_KT) / BA_KT;     // keys 0 .. pos1
+    const int* tbl = p.table + (size_t)slot * p.stride;
+    const int nrg = nq * rep;                      // rows of one key / value head
+    const int nblk = (nrg + BA_RB - 1) / BA_RB;    // row blocks of one head
+    for (int ti = rank; ti < ntiles; ti += CL) {
+        const int j0 = ti * BA_KT, nk = min(BA_KT, pos1 + 1 - j0), jl = j0 + lane;
+        for (int c0 = 0; c0 < G; c0 += p.gt) {
+            const int gn = min(p.gt, G - c0);
+            __syncthreads();                       // the tile buffers are free (and the rows are initialised)
+            ba_load_tiles(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, (size_t)G * dk + (size_t)c0 * dv, dv, sK, tsk, sV, tsv, gn, nk, j0, vec);
+            for (int it = warp; it < gn * nblk; it += nw) {
+                const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * BA_RB, nr = min(BA_RB, nrg - rr0);
+                int rows[BA_RB];
+                const float* qv[BA_RB];
+#pragma unroll
+                for (int b = 0; b < BA_RB; ++b) {
+                    const int rr = rr0 + min(b, nr - 1);
+                    rows[b] = (rr / rep) * H + c * rep + rr % rep;
+                    qv[b] = sQ + (size_t)rows[b] * dk;
+                }
+                // ---- scores of the warp's rows against key `lane` ----
+                float sc[BA_RB] = {0.f, 0.f, 0.f, 0.f};
+                if (lane < nk) {
+                    const float* kv = sK + ((size_t)cl_ * BA_KT + lane) * tsk;
+                    if (vec) {
+                        const float4* k4 = reinterpret_cast<const float4*>(kv);
+#pragma unroll 4
+                        for (int i = 0; i < dk / 4; ++i) {
+                            const float4 kx = k4[i];
+#pragma unroll
+                            for (int b = 0; b < BA_RB; ++b) {
+                                const float4 qx = reinterpret_cast<const float4*>(qv[b])[i];
+                                sc[b] = fmaf(qx.x, kx.x, sc[b]); sc[b] = fmaf(qx.y, kx.y, sc[b]);
+                                sc[b] = fmaf(qx.z, kx.z, sc[b]); sc[b] = fmaf(qx.w, kx.w, sc[b]);
+                            }
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int i = 0; i < dk; ++i) {
+                            const float kx = kv[i];
+#pragma unroll
+                            for (int b = 0; b < BA_RB; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
+                        }
+                    }
+                }
+                // ---- running maximum / sum of every row, the tile's weights ----
+#pragma unroll
+                for (int b = 0; b < BA_RB; ++b) {
+                    if (b >= nr) break;
+                    const int r = rows[b], pq = pos0 + r / H, h = r % H;
+                    const bool vis = lane < nk && jl <= pq;
+                    const float s = vis ? sc[b] + p.bias[(size_t)min(pq - jl, p.nb) * H + h] : -CUDART_INF_F;
+                    float mx = s;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    const float mo = sMax[r], mn = fmaxf(mo, mx);
+                    float e = vis ? expf(s - mn) : 0.f;        // mn is finite wherever a key is visible
+                    sP[r * BA_KT + lane] = e;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
+                    __syncwarp();                              // everyone has read the old maximum
+                    if (lane == 0) {
+                        const float scl = mo > -CUDART_INF_F ? expf(mo - mn) : 0.f;
+                        sScl[r] = scl;
+                        sSum[r] = sSum[r] * scl + e;
+                        sMax[r] = mn;
+                    }
+                }
+                __syncwarp();
+                // ---- weights x values ----
+                const float* vt = sV + (size_t)cl_ * BA_KT * tsv;
+                for (int d = lane; d < dv; d += 32) {
+                    float acc[BA_RB];
+#pragma unroll
+                    for (int b = 0; b < BA_RB; ++b) acc[b] = sO[(size_t)rows[b] * dv + d] * sScl[rows[b]];
+#pragma unroll 2
+                    for (int kt = 0; kt < BA_KT; kt += 4) {
+                        const float v0 = vt[(kt + 0) * tsv + d], v1 = vt[(kt + 1) * tsv + d], v2 = vt[(kt + 2) * tsv + d], v3 = vt[(kt + 3) * tsv + d];
+#pragma unroll
+                        for (int b = 0; b < BA_RB; ++b) {
+                            const float4 w4 = *reinterpret_cast<const float4*>(sP + rows[b] * BA_KT + kt);
+                            acc[b] = fmaf(w4.x, v0, acc[b]); acc[b] = fmaf(w4.y, v1, acc[b]);
+                            acc[b] = fmaf(w4.z, v2, acc[b]); acc[b] = fmaf(w4.w, v3, acc[b]);
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < BA_RB; ++b)
+                        if (b < nr) sO[(size_t)rows[b] * dv + d] = acc[b];
+                }
+                __syncwarp();
+            }
+        }
+    }
+    // the CTAs' partial results merged in rank order; every CTA finishes its share of the outputs
+    cluster.sync();
+    for (int e = rank * (int)blockDim.x + threadIdx.x; e < R * dv; e += CL * (int)blockDim.x) {
+        const int r = e / dv, d = e % dv;
+        float m = -CUDART_INF_F;
+        for (int rk = 0; rk < CL; ++rk) m = fmaxf(m, cluster.map_shared_rank(sMax, rk)[r]);
+        float num = 0.f, den = 0.f;
+        for (int rk = 0; rk < CL; ++rk) {
+            const float mr = cluster.map_shared_rank(sMax, rk)[r];
+            if (mr > -CUDART_INF_F) {
+                const float f = expf(mr - m);
+                num = fmaf(cluster.map_shared_rank(sO, rk)[e], f, num);
+                den = fmaf(cluster.map_shared_rank(sSum, rk)[r], f, den);
+            }
+        }
+        p.out[(size_t)(t0 + r / H) * p.ldo + (size_t)(r % H) * dv + d] = num / den;
+    }
+    cluster.sync();                                // nobody leaves while its shared memory is still being read
+}
+
+}  // namespace b200

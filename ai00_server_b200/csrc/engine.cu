@@ -38,6 +38,8 @@
 #include "retention.cuh"
 #include "delta_rule.cuh"
 #include "window_attn.cuh"
+#include "bias_attn.cuh"
+#include "hyper.cuh"
 
 namespace b200 {
 
@@ -289,11 +291,13 @@ static b200rwkv_info derive_info(const StFile& st) {
     memset(&o, 0, sizeof(o));
     if (st.find("embed") && st.find("final.norm")) {      // families whose layer sizes are in a config.json
         const StTensor& e = *st.find("embed");
-        // Kemirax norms are one gain; Degavik norms are weight vectors (and a layer may have no tensors of its own)
-        o.version = st.find("final.norm")->numel() == 1 ? B200RWKV_ARCH_KEMIRAX : B200RWKV_ARCH_DEGAVIK;
+        // Kemirax norms are one gain; Degavik norms are weight vectors (and a layer may have no tensors of its own); Zufulix
+        // norms have a bias and the embedding table doubles as the output matrix
+        o.version = st.find("final.norm.b") ? B200RWKV_ARCH_ZUFULIX
+                                            : (st.find("final.norm")->numel() == 1 ? B200RWKV_ARCH_KEMIRAX : B200RWKV_ARCH_DEGAVIK);
         o.num_vocab = (int)StFile::dim(e, 0, "embed", 2);
         o.num_emb = (int)StFile::dim(e, 1, "embed", 2);
-        if (o.version == B200RWKV_ARCH_KEMIRAX) {
+        if (o.version != B200RWKV_ARCH_DEGAVIK) {
             while (st.find("l" + std::to_string(o.num_layer) + ".norm1")) ++o.num_layer;
         } else {                                           // layers that own tensors (the config lists the rest)
             for (int i = 0, miss = 0; miss < 64; ++i) {
@@ -413,6 +417,7 @@ struct Snapshot { float* buf = nullptr; float* logits = nullptr; size_t bytes = 
 
 #include "kemirax.cuh"
 #include "degavik.cuh"
+#include "zufulix.cuh"
 
 using namespace b200;
 
@@ -523,6 +528,8 @@ struct b200rwkv_engine {
     void kx_load(const StFile& st, KxSizes& z);
     void dg_load(const StFile& st, KxSizes& z);                   // Degavik family (degavik_engine.cuh)
     void dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
+    void zf_load(const StFile& st, KxSizes& z);                   // Zufulix family (zufulix_engine.cuh)
+    void zf_enqueue_layers(cudaStream_t s, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
     __nv_bfloat16* kx_up16(const std::vector<uint16_t>& v);
     float* kx_up32(const std::vector<float>& v);
     void kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact = false);
@@ -1830,6 +1837,7 @@ void b200rwkv_engine::state_xform(int slot, bool import, float* snap) {
 
 #include "kemirax_engine.cuh"
 #include "degavik_engine.cuh"
+#include "zufulix_engine.cuh"
 
 // =========================================================================================
 // in-process tensor-parallel group

@@ -106,8 +106,8 @@ private:
 // ------------------------------------------------------------------------------------------------------------------
 struct RotCfg { int dims = 0; double base = 10000.0; bool scaled = false; double factor = 1, original = 0, fast = 0, slow = 0; };
 
-enum KxMixer { KX_LATENT = 0, KX_GLA = 1, KX_RETENTION = 2, KX_DELTA = 3, KX_WINDOW = 4 };
-enum KxFamily { KX_FAMILY_KEMIRAX = 0, KX_FAMILY_DEGAVIK = 1 };
+enum KxMixer { KX_LATENT = 0, KX_GLA = 1, KX_RETENTION = 2, KX_DELTA = 3, KX_WINDOW = 4, KX_BIASED = 5 };
+enum KxFamily { KX_FAMILY_KEMIRAX = 0, KX_FAMILY_DEGAVIK = 1, KX_FAMILY_ZUFULIX = 2 };
 
 struct KxLayerCfg {
     int mixer = KX_LATENT;
@@ -119,7 +119,11 @@ struct KxLayerCfg {
     float softcap = 0.f;
     std::vector<double> decay;                                   // retention: one per head
     int weights_of = -1;                                         // the layer whose tensors this layer uses (-1: its own)
-    bool mlp_dense = false;                                      // feed-forward is one gated unit, not routed experts
+    bool mlp_dense = false;                                      // feed-forward is one dense unit, not routed experts
+    // Zufulix (zufulix.cuh): attention with a bias per (distance bucket, head), blended values, grouped sigmoid router
+    double bias_max = 0;                                         // distance from which every key shares the last bucket
+    bool v_mix = false;                                          // values blended with the first such layer's
+    int groups = 0, groups_keep = 0;                             // router: groups of neighbouring experts / groups kept (0: none)
     int rot_dim = 0, kv_rank = 0, q_rank = 0, kv_from = -1;     // latent attention
     float scale = 1.f;
     RotCfg rot;
@@ -136,10 +140,13 @@ struct KxConfig {
     int family = KX_FAMILY_KEMIRAX;
     int vocab = 0, width = 0;
     float eps = 1e-5f;
+    int streams = 0;                                             // copies of the residual (0: the plain residual)
+    float embed_scale = 1.f;                                     // factor on the embedding row
     std::vector<KxLayerCfg> layers;
 };
 
 static KxConfig dg_parse_config(const JVal& root);
+static KxConfig zf_parse_config(const JVal& root);
 
 // model registry of the families that come with a config.json: `architecture` names the design
 static KxConfig kx_parse_config(const char* json, size_t n) {
@@ -148,6 +155,7 @@ static KxConfig kx_parse_config(const char* json, size_t n) {
     REQUIRE(root.has("architecture") && root.at("architecture").kind == JVal::STR, B200RWKV_ERR_INVALID, "config: no architecture");
     const std::string arch = root.at("architecture").str;
     if (arch == "Degavik") return dg_parse_config(root);
+    if (arch == "Zufulix") return zf_parse_config(root);
     REQUIRE(arch == "Kemirax", B200RWKV_ERR_UNSUPPORTED, "config: unknown architecture '" + arch + "'");
     KxConfig c;
     c.vocab = root.integer("vocab");
@@ -251,6 +259,12 @@ struct KxLayer {
     int wa_gt = 1;                                               // key / value heads per tile load of the attention kernel
     float* rec_state = nullptr;                                  // retention / delta rule: [S][H][dk][dv]
     int cache_D = 0;                                             // floats per cached token when the layer owns a pool
+    // Zufulix: layer norms with bias, stream coefficients of the two sublayers, projection biases, distance-bias table
+    float *norm1_b = nullptr, *norm2_b = nullptr;
+    float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
+    float *proj_b = nullptr, *rel_bias = nullptr;                // [proj_n], [rel_n + 1][H]
+    int rel_n = 0, vmode = 0;
+    float lam = 0.f;
     // per-sequence memory of fixed size, in the order of the flat state record
     struct Block { float* base; size_t per_slot; };
     std::vector<Block> fixed;
@@ -259,7 +273,7 @@ struct KxLayer {
 // largest per-token widths of the activation buffers over the layers of a model (filled by the family's loader)
 struct KxSizes {
     size_t n_cq = 1, n_q = 1, n_qa = 1, n_kv = 1, n_part = 1, n_olat = 1, n_vout = 1, n_pr = 1, n_z = 1, n_rl = 1, n_yc = 1, n_ys = 1,
-           n_cv = 1, n_gl = 1;
+           n_cv = 1, n_gl = 1, n_vf = 1, n_streams = 1;
     int max_top = 1, max_E = 1;
 };
 
@@ -271,6 +285,9 @@ struct SeqModel {
     int W = 0, V = 0, page = 64, npages = 0, state_ctx = 0;
     float final_gain = 1.f;
     float* final_w = nullptr;                     // weight vector of the last norm (families that have one)
+    float* final_b = nullptr;                     // its bias (layer-norm families)
+    int streams = 1;                              // copies of the residual a token row of x holds
+    float* vfirst = nullptr;                      // [T, G * dv] values of the first blending attention layer, this step's tokens
     int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
     int wa_ctas_prompt = 1, wa_ctas_decode = 1;   // windowed-attention CTAs one SM holds at once (prompt / decode shape)
     float *y = nullptr, *cv = nullptr, *gl = nullptr;   // sublayer output, convolution output, output-gate logits

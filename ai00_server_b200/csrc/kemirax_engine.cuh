@@ -192,7 +192,7 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.W = m.cfg.width; m.V = m.cfg.vocab;
     const int W = m.W, nl = (int)m.cfg.layers.size();
     memset(&info, 0, sizeof(info));
-    info.version = m.cfg.family == KX_FAMILY_DEGAVIK ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_KEMIRAX; info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
+    info.version = m.cfg.family == KX_FAMILY_ZUFULIX ? B200RWKV_ARCH_ZUFULIX : (m.cfg.family == KX_FAMILY_DEGAVIK ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_KEMIRAX); info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
     L = nl; C = W; V = m.V; Vl = V; Cl = C; H = Hl = 0; N = 0; F = Fl = 0;
     REQUIRE(world == 1, B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json run on one GPU in this version");
     REQUIRE(quant_layers == 0 && loras.empty(), B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json take no LoRA / quantised layers");
@@ -224,19 +224,20 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     for (int i = m.npages - 1; i >= 0; --i) m.free_pages.push_back(i);
 
     KxSizes z;
-    if (m.cfg.family == KX_FAMILY_DEGAVIK) dg_load(st, z);
+    if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_load(st, z);
+    else if (m.cfg.family == KX_FAMILY_DEGAVIK) dg_load(st, z);
     else kx_load(st, z);
     emb = nullptr;
 
     // ---- activations (maxT rows each) ----
     const size_t T_ = (size_t)maxT;
     auto fa = [&](size_t n) { return (float*)dalloc(n * 4); };
-    m.x = fa(T_ * W); m.h = fa(T_ * W); m.hs = fa(T_ * W); m.G = fa(T_ * 2 * W); m.hn = fa(T_ * W);
+    m.x = fa(T_ * W * z.n_streams); m.h = fa(T_ * W); m.hs = fa(T_ * W); m.G = fa(T_ * 2 * W); m.hn = fa(T_ * W);
     m.cq = fa(T_ * z.n_cq); m.q = fa(T_ * z.n_q); m.qa = fa(T_ * z.n_qa); m.kv = fa(T_ * z.n_kv); m.part = fa(T_ * z.n_part);
     m.olat = fa(T_ * z.n_olat); m.vout = fa(T_ * z.n_vout); m.pr = fa(T_ * z.n_pr); m.z = fa(T_ * z.n_z);
     m.rl = fa(T_ * z.n_rl); m.wgt = fa(T_ * z.max_top); m.yc = fa(T_ * z.max_top * z.n_yc); m.dn = fa(T_ * z.max_top * W);
     m.ys = fa(T_ * z.n_ys); m.ds = fa(T_ * W);
-    m.y = fa(T_ * W); m.cv = fa(T_ * z.n_cv); m.gl = fa(T_ * z.n_gl);
+    m.y = fa(T_ * W); m.cv = fa(T_ * z.n_cv); m.gl = fa(T_ * z.n_gl); m.vfirst = fa(T_ * z.n_vf);
     m.lin_ws_floats = (size_t)4 << 20;                   // split-k partial sums of one projection launch
     m.lin_ws = fa(m.lin_ws_floats);
     m.sel = (int*)dalloc(T_ * z.max_top * 4); m.row_of = (int*)dalloc(T_ * z.max_top * 4); m.list = (int*)dalloc(T_ * z.max_top * 4);
@@ -318,11 +319,12 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
     {
         PageUpdateParams pu{m.sm, m.d_table, m.npages};
         launch_k(page_update_kernel, dim3(1), dim3(128), 0, pu, KC_OTHER, s, prof);
-        EmbedRowsParams ep{m.embed, m.x, W, mv};
+        EmbedRowsParams ep{m.embed, m.x, W, mv, m.cfg.embed_scale, m.streams};
         launch_k(embed_rows_kernel, dim3(rows), dim3(NORM_THREADS), 0, ep, KC_LN, s, prof);
     }
     const int nslot_grid = std::min(S, rows);
-    for (size_t li = 0; li < m.layers.size(); ++li) {
+    if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_enqueue_layers(s, rows, nslot_grid, decode, nsplit, prof);    // ends with the last norm
+    for (size_t li = 0; li < m.layers.size() && m.cfg.family != KX_FAMILY_ZUFULIX; ++li) {
         KxLayer& l = m.layers[li];
         const KxLayerCfg& c = l.c;
         if (m.cfg.family == KX_FAMILY_DEGAVIK) {
@@ -415,8 +417,10 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         if (m.dbg_layers && !use_graph)
             CK(cudaMemcpyAsync(m.dbg_layers + li * (size_t)maxT * W, m.x, (size_t)maxT * W * 4, cudaMemcpyDeviceToDevice, s));
     }
-    FinalNormParams fn{m.x, m.hn, d_hidden, m.final_gain, m.cfg.eps, W, mv, m.final_w};
-    launch_k(final_norm_kernel, dim3(rows), dim3(NORM_THREADS), 0, fn, KC_LN, s, prof);
+    if (m.cfg.family != KX_FAMILY_ZUFULIX) {
+        FinalNormParams fn{m.x, m.hn, d_hidden, m.final_gain, m.cfg.eps, W, mv, m.final_w};
+        launch_k(final_norm_kernel, dim3(rows), dim3(NORM_THREADS), 0, fn, KC_LN, s, prof);
+    }
     if (rrows > 0) {
         LinParams ph = lin(m.hn, W, m.head, d_logits, V, V, W);
         ph.cnt = cntR;
@@ -478,10 +482,12 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
         const int ctas = std::max(1, nch * hg_min), tiles = cdiv(ctx_max, LA_KT);
         while (ns < m.max_split && ctas * ns < 2 * num_sms && tiles / (ns * 2) >= 2) ns *= 2;
     }
-    if (m.cfg.family == KX_FAMILY_DEGAVIK) {               // CTAs per attention chunk (a cluster): the keys a chunk can see, in tiles
+    if (m.cfg.family != KX_FAMILY_KEMIRAX) {               // CTAs per attention chunk (a cluster): the keys a chunk can see, in tiles
         int seen = 0;
-        for (const KxLayer& l : m.layers)
+        for (const KxLayer& l : m.layers) {
             if (l.c.mixer == KX_WINDOW) seen = std::max(seen, std::min(ctx_max, l.c.window + l.c.keep_first + QB));
+            if (l.c.mixer == KX_BIASED) seen = std::max(seen, ctx_max);
+        }
         const int tiles = cdiv(seen, WA_KT);
         ns = 1;
         const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt);         // CTAs the GPU holds at once

@@ -14,7 +14,7 @@
 //   lin_skinny_kernel        exact precision, a few rows: one warp per output pair, weight rows streamed as 16-byte loads, f32
 //                            FMA.
 //
-// Epilogues (fused): bias, sigmoid / silu, a per-row scale, accumulate-into-residual through a gate, and the gated units
+// Epilogues (fused): bias, sigmoid / silu / erf-gelu / squared relu, a per-row scale, accumulate-into-residual through a gate, and the gated units
 // (clamped, or plain silu(g) * u) on interleaved (gate, up) output pairs.
 #pragma once
 #include <cuda_bf16.h>
@@ -29,6 +29,8 @@ enum LinEpi {
     LE_GATED_ADD = 2,   // Y += gate[r, n] * acc          (residual accumulate; every element has one writer)
     LE_GLU_CLAMP = 3,   // outputs (2i, 2i+1) = (g, u): Y[r, i] = min(g, lim) * sigmoid(1.702 min(g, lim)) * (clamp(u, -lim, lim) + 1)
     LE_GLU_SILU = 4,    // outputs (2i, 2i+1) = (g, u): Y[r, i] = g * sigmoid(g) * u
+    LE_GELU_ERF = 5,    // Y = a * Phi(a), a = acc + bias, Phi the normal distribution function (erf form)
+    LE_RELU_SQ = 6,     // Y = max(acc + bias, 0)^2
 };
 
 struct LinParams {
@@ -79,6 +81,8 @@ __device__ __forceinline__ void lin_store(const LinParams& p, int g, int yrow, i
         if (b) a += b[nn];
         float* y = Y + (size_t)yrow * p.ldy + nn;
         if (p.epi == LE_SIGMOID) *y = lin_sigmoid(a);
+        else if (p.epi == LE_GELU_ERF) *y = 0.5f * a * (1.f + erff(a * 0.70710678118654752f));
+        else if (p.epi == LE_RELU_SQ) { const float r = fmaxf(a, 0.f); *y = r * r; }
         else if (p.epi == LE_GATED_ADD) *y += p.gate[(size_t)yrow * p.ldg + nn] * a;
         else *y = a;
     }

@@ -27,15 +27,41 @@ struct MoeRouteParams {
     int* sel;                                 // [T][top] expert index
     float* wgt;                               // [T][top]
     MetaView meta;
-    int mode = 0;                             // MOE_SOFTMAX_ALL | MOE_TOP_LOGITS
+    int mode = 0;                             // MOE_SOFTMAX_ALL | MOE_TOP_LOGITS | MOE_SIGMOID_GROUPS
+    int groups = 0, keep = 0;                 // MOE_SIGMOID_GROUPS: equal groups of neighbouring experts, groups that stay eligible (0: no groups)
 };
 
 // MOE_SOFTMAX_ALL: probabilities over all outputs, choice by probability + bias, weights = the chosen probabilities as they are.
 // MOE_TOP_LOGITS:  bias is part of the logits; the `top` largest logits are chosen, weights = softmax over the chosen logits only.
-enum MoeRouteMode { MOE_SOFTMAX_ALL = 0, MOE_TOP_LOGITS = 1 };
+// MOE_SIGMOID_GROUPS: scores = sigmoid(logit); a group of neighbouring experts is judged by the sum of its two largest scores and
+//                  only experts of the `keep` best groups are eligible; the `top` largest eligible scores are chosen, weights =
+//                  the chosen scores over their sum.
+enum MoeRouteMode { MOE_SOFTMAX_ALL = 0, MOE_TOP_LOGITS = 1, MOE_SIGMOID_GROUPS = 2 };
 
 constexpr int MOE_ROUTE_THREADS = 256;
-__host__ __device__ inline size_t moe_route_smem(int K, int NE) { return ((size_t)K + NE) * sizeof(float); }
+__host__ __device__ inline size_t moe_route_smem(int K, int NE) { return ((size_t)K + 3 * (size_t)NE) * sizeof(float); }
+
+// warp-wide arg-max over a[0 .. n) in shared memory (ties: lower index); the winner's entry becomes -inf so that the next call
+// finds the runner-up.  Every lane returns the same (index, value).
+__device__ __forceinline__ int moe_warp_take_max(float* a, int n, float& val) {
+    const int lane = threadIdx.x & 31;
+    float best = -CUDART_INF_F; int bi = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+        const float c = a[e];
+        if (c > best || (c == best && e < bi)) { best = c; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    __syncwarp();
+    if (lane == 0 && bi < n) a[bi] = -CUDART_INF_F;
+    __syncwarp();
+    val = best;
+    return bi;
+}
 
 // One CTA per token: router logits in f32 on the f32 row (every warp takes outputs warp, warp + 8, ...), then warp 0 turns them
 // into the choice: softmax, + selection bias, `top` largest, weights = the unbiased probabilities.
@@ -72,6 +98,45 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(const MoeR
     }
     __syncthreads();
     if (warp != 0) return;
+    if (p.mode == MOE_SIGMOID_GROUPS) {
+        float* ms = z + p.NE;                 // [NE] scores still eligible (-inf: not, or already chosen)
+        float* gs = ms + p.NE;                // [groups] group scores; a kept group's entry ends as -inf
+        for (int e = lane; e < p.NE; e += 32) { const float s = 1.f / (1.f + expf(-z[e])); z[e] = s; ms[e] = s; }
+        __syncwarp();
+        if (p.groups > 0) {
+            const int per = p.NE / p.groups;
+            for (int g = lane; g < p.groups; g += 32) {
+                float a = -CUDART_INF_F, b = -CUDART_INF_F;          // the two largest of the group
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    const float s = z[e];
+                    if (s > a) { b = a; a = s; } else if (s > b) b = s;
+                }
+                gs[g] = per > 1 ? a + b : a;
+            }
+            __syncwarp();
+            for (int k = 0; k < p.keep; ++k) {             // taking a maximum leaves -inf in its place (every score is finite)
+                float v;
+                (void)moe_warp_take_max(gs, p.groups, v);
+            }
+            for (int e = lane; e < p.NE; e += 32)
+                if (gs[e / per] != -CUDART_INF_F) ms[e] = -CUDART_INF_F;   // its group was not kept
+            __syncwarp();
+        }
+        int idx[MOE_MAX_TOP];
+        float sc[MOE_MAX_TOP], sum = 0.f;
+        for (int k = 0; k < p.top; ++k) {
+            float v;
+            idx[k] = moe_warp_take_max(ms, p.NE, v);
+            sc[k] = z[min(idx[k], p.NE - 1)];
+            sum += sc[k];
+        }
+        if (lane == 0)
+            for (int k = 0; k < p.top; ++k) {
+                p.sel[(size_t)t * p.top + k] = idx[k];
+                p.wgt[(size_t)t * p.top + k] = sc[k] / (sum + 1e-20f);
+            }
+        return;
+    }
     if (p.mode == MOE_TOP_LOGITS) {
         unsigned long long taken = 0ull;
         float zs[MOE_MAX_TOP];

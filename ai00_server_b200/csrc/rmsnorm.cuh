@@ -1,5 +1,5 @@
 // Root-mean-square normalisation stages on f32 rows (every norm of this family is computed in 32-bit):
-//   embed_rows_kernel      x[t] = table[token[t]]                                   (bf16 table -> f32 residual)
+//   embed_rows_kernel      x[t] = table[token[t]] * scale, written to every copy of the residual   (bf16 table -> f32 residual)
 //   norm_shift_kernel      h = x / rms(x) * g (one scalar gain);  hs = h + (h_prev - h) * mu  (token shift on the NORMED row;
 //                          h_prev = the previous token's h: the row before it in this step, or the sequence's shift state);
 //   shift_commit_kernel    the last token of every sequence in the step leaves its h as the new shift state
@@ -33,14 +33,19 @@ struct EmbedRowsParams {
     float* x;
     int W;
     MetaView meta;
+    float scale = 1.f;       // factor on the row
+    int copies = 1;          // the row is written `copies` times: x is [T][copies][W]
 };
 
 __global__ void __launch_bounds__(NORM_THREADS) embed_rows_kernel(const EmbedRowsParams p) {
     const int t = blockIdx.x;
     if (t >= p.meta.T()) return;
     const __nv_bfloat16* src = p.table + (size_t)p.meta.tok()[t] * p.W;
-    float* dst = p.x + (size_t)t * p.W;
-    for (int c = threadIdx.x; c < p.W; c += blockDim.x) dst[c] = __bfloat162float(src[c]);
+    float* dst = p.x + (size_t)t * p.copies * p.W;
+    for (int c = threadIdx.x; c < p.W; c += blockDim.x) {
+        const float v = __bfloat162float(src[c]) * p.scale;
+        for (int s = 0; s < p.copies; ++s) dst[(size_t)s * p.W + c] = v;
+    }
 }
 
 struct NormShiftParams {

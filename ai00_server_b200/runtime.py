@@ -235,7 +235,7 @@ class Model:
         lora: list of (st_bytes, alpha) blended at load (reference lib.rs:466-485);
         quant / quant_type: the reload request's fields (lib.rs:211-215): the first `quant` layers in "Int8" or "NF4";
         rank / world: one process per GPU instead (b200rwkv_create_tp + tp.connect);
-        config: text of the model's config.json for families that come with one (architecture "Kemirax" or "Degavik"); kv_tokens / kv_page:
+        config: text of the model's config.json for families that come with one (architecture "Kemirax", "Degavik" or "Zufulix"); kv_tokens / kv_page:
         capacity (tokens over all live sequences) and page size of their attention cache."""
         if isinstance(quant_type, str):
             kinds = {"none": capi.QUANT_NONE, "int8": capi.QUANT_INT8, "nf4": capi.QUANT_NF4, "sf4": 3}

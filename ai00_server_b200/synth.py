@@ -484,3 +484,84 @@ def make_degavik(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e
     bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
     rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
     return json.dumps(cfg).encode(), pack_st_bf16(t), rounded
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Zufulix family (config.json + bf16 safetensors): random weights for tests and bench.py
+# ----------------------------------------------------------------------------------------------------------------------
+def zufulix_layer(*, heads=4, kv_heads=None, dim=16, vdim=16, scale=None, bias_max=40, v_mix=True, mlp="dense", ff=48, experts=8, top=2,
+                  groups=(4, 2)) -> dict:
+    """One entry of config['layers'] (attention mixer).  mlp: 'dense' | 'moe' | None; groups: (count, keep) or None."""
+    mixer = {"heads": heads, "kv_heads": int(kv_heads or heads), "dim": dim, "vdim": vdim,
+             "scale": float(scale if scale is not None else dim ** -0.5), "bias_max": bias_max}
+    if v_mix is not None:
+        mixer["v_mix"] = bool(v_mix)
+    layer = {"type": "attention", "mixer": mixer, "mlp": None}
+    if mlp == "dense":
+        layer["mlp"] = {"kind": "dense", "ff": int(ff)}
+    elif mlp == "moe":
+        router = {"experts": int(experts), "top": int(top)}
+        if groups:
+            router["groups"] = {"count": int(groups[0]), "keep": int(groups[1])}
+        layer["mlp"] = {"kind": "moe", "router": router, "expert": {"ff": int(ff)}}
+    return layer
+
+
+def make_zufulix(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, streams: int | None = 3,
+                 embed_scale: float | None = 0.7, rel_rows: int = 12, arrays: bool = True, rel_gain: float = 1.0):
+    """(config.json bytes, safetensors image, dict of float64 arrays holding the bf16-rounded values, or None when `arrays` is
+    off) for a random model of the family.  streams None: the plain residual (no stream tensors)."""
+    rng = np.random.default_rng(seed)
+    W = width
+    t = {}
+
+    def mat(n, k, g=1.0):
+        return (rng.standard_normal((n, k)) * (g / np.sqrt(k))).astype(np.float32)
+
+    def norm(name):
+        t[name] = rng.uniform(0.5, 1.5, W).astype(np.float32)
+        t[name + ".b"] = (0.2 * rng.standard_normal(W)).astype(np.float32)
+
+    t["embed"] = rng.standard_normal((vocab, W)).astype(np.float32)
+    for i, l in enumerate(layers):
+        p, m = "l%d." % i, l["mixer"]
+        H, dk, dv = m["heads"], m["dim"], m["vdim"]
+        G = m.get("kv_heads", H)
+        norm(p + "norm1")
+        for n, rows in (("q", H * dk), ("k", G * dk), ("v", G * dv)):
+            t[p + "mix." + n] = mat(rows, W, 2.0 if n in "qk" else 1.0)
+            t[p + "mix." + n + ".b"] = (0.3 * rng.standard_normal(rows)).astype(np.float32)
+        t[p + "mix.rel"] = (rel_gain * rng.standard_normal((rel_rows, H))).astype(np.float32)
+        t[p + "mix.vmix"] = np.float32(rng.uniform(0.2, 0.8))
+        t[p + "mix.o"] = mat(W, H * dv)
+        f = l.get("mlp")
+        subs = [1]
+        if f:
+            subs.append(2)
+            norm(p + "norm2")
+            if f["kind"] == "dense":
+                t[p + "mlp.up"] = mat(f["ff"], W, 2.0)
+                t[p + "mlp.down"] = mat(W, f["ff"])
+            else:
+                E = f["router"]["experts"]
+                t[p + "mlp.router"] = mat(E, W, 3.0)
+                for e in range(E):
+                    t[p + "mlp.e%d.up" % e] = mat(f["expert"]["ff"], W, 2.0)
+                    t[p + "mlp.e%d.down" % e] = mat(W, f["expert"]["ff"])
+        if streams is not None:
+            for q in subs:
+                hp = p + "hc%d." % q
+                t[hp + "in"] = (np.full(streams, 1.0 / streams) + 0.2 * rng.standard_normal(streams)).astype(np.float32)
+                t[hp + "out"] = rng.uniform(0.5, 1.2, streams).astype(np.float32)
+                t[hp + "mix"] = (np.eye(streams) + 0.15 * rng.standard_normal((streams, streams))).astype(np.float32)
+    norm("final.norm")
+    cfg = {"architecture": "Zufulix", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": W}
+    if streams is not None:
+        cfg["streams"] = int(streams)
+    if embed_scale is not None:
+        cfg["embedding"] = {"scale": float(embed_scale)}
+    if not arrays:
+        return json.dumps(cfg).encode(), pack_st_bf16(t), None
+    bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
+    rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
+    return json.dumps(cfg).encode(), pack_st_bf16(t), rounded

@@ -115,6 +115,7 @@ typedef struct {
 } b200rwkv_options;
 #define B200RWKV_ARCH_KEMIRAX 100     /* b200rwkv_info.version of that family (num_head / head_size are per layer there: 0) */
 #define B200RWKV_ARCH_DEGAVIK 101
+#define B200RWKV_ARCH_ZUFULIX 102
 #define B200RWKV_QUANT_NONE 0
 #define B200RWKV_QUANT_INT8 1         /* blocks of 128 inputs: f16 (min, max) + 8-bit codes */
 #define B200RWKV_QUANT_NF4 2          /* blocks of 64 inputs: f16 absmax + 4-bit NormalFloat codes */
