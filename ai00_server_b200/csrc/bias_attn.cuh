@@ -17,8 +17,9 @@
 //                           the 32-key tiles up to the chunk's last position are dealt out among the cluster's CTAs; every CTA
 //                           walks its tiles ONCE with a running maximum / sum per (token, head) row (online softmax) and the
 //                           CTAs' partial results are merged through distributed shared memory in rank order.  A warp owns
-//                           four rows of one key / value head: it scores them against a key per lane, then applies the tile's
-//                           weights to the values, with no CTA barrier in between.  Scores, weights and sums in f32.
+//                           1, 2 or 4 rows of one key / value head (template): it scores them against a key per lane, then
+//                           applies the tile's weights to the values, with no CTA barrier in between; the next tiles arrive by
+//                           cp.async into a second buffer meanwhile.  Scores, weights and sums in f32.
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
@@ -88,16 +89,17 @@ struct BiasAttnParams {
 
 constexpr int BA_KT = 32;                          // keys per tile (one per lane in the score phase)
 constexpr int BA_THREADS = 512;                    // most threads per CTA; the host launches 256 where fewer warps find work
-constexpr int BA_RB = 4;                           // rows of one key / value head a warp works on together
+constexpr int BA_RB = 4;                           // most rows of one key / value head a warp works on together (kernel template: 1, 2, 4)
 
 __host__ __device__ inline size_t bias_attn_smem(int qb, int H, int dk, int dv, int gt) {
     const size_t R = (size_t)qb * H;
-    return (R * dk + R * dv + R * BA_KT + (size_t)gt * BA_KT * (dk + 4 + dv + 4) + 3 * R + 8) * sizeof(float);
+    return (R * dk + R * dv + R * BA_KT + 2 * (size_t)gt * BA_KT * (dk + 4 + dv + 4) + 3 * R + 8) * sizeof(float);      // two tile buffers
 }
 
 // `nk` cache rows from position j0 on: `wk` floats at offset `offk` and `wv` floats at offset `offv` of each of `gn` consecutive
 // heads -> tk[head][key][tsk], tv[head][key][tsv]; value rows past nk are zero (their weights are zero too, and 0 * junk must
-// stay 0).  vec: 16-byte cp.async copies, a warp per cache row, all copies of the tile in flight together.
+// stay 0).  vec: 16-byte cp.async copies, a warp per cache row, all copies of the tile in flight together.  Ends with a commit
+// of the copies it issued (an empty group on the scalar path); the caller waits.
 __device__ __forceinline__ void ba_load_tiles(const float* cache, const int* tbl, int page, int D, size_t offk, int wk, size_t offv, int wv,
                                               float* tk, int tsk, float* tv, int tsv, int gn, int nk, int j0, bool vec) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (int)(blockDim.x >> 5);
@@ -121,13 +123,10 @@ __device__ __forceinline__ void ba_load_tiles(const float* cache, const int* tbl
             }
         }
     }
-    if (vec) {
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
 }
 
+template <int RBT>
 __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnParams p) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -145,9 +144,9 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
     extern __shared__ __align__(16) float ba_smem[];
     const int Rcap = p.qb * H;
     float* sP = ba_smem;                           // [R][KT] weights of the tile (rows start on 16 bytes for any head size)
-    float* sK = sP + (size_t)Rcap * BA_KT;         // [gt][KT][tsk]
-    float* sV = sK + (size_t)p.gt * BA_KT * (dk + 4);   // [gt][KT][tsv]
-    float* sQ = sV + (size_t)p.gt * BA_KT * (dv + 4);   // [R][dk]
+    float* sK = sP + (size_t)Rcap * BA_KT;         // [2][gt][KT][tsk]
+    float* sV = sK + 2 * (size_t)p.gt * BA_KT * (dk + 4);   // [gt][KT][tsv], two buffers each: a round's tiles arrive while the
+    float* sQ = sV + 2 * (size_t)p.gt * BA_KT * (dv + 4);   // [R][dk]                 previous round is multiplied
     float* sO = sQ + (size_t)Rcap * dk;            // [R][dv] un-normalised outputs
     float* sMax = sO + (size_t)Rcap * dv;          // [R] running maximum / sum / last rescale of this CTA
     float* sSum = sMax + Rcap;
@@ -161,34 +160,56 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
     const int ntiles = (pos1 + BA_KT) / BA_KT;     // keys 0 .. pos1
     const int* tbl = p.table + (size_t)slot * p.stride;
     const int nrg = nq * rep;                      // rows of one key / value head
-    const int nblk = (nrg + BA_RB - 1) / BA_RB;    // row blocks of one head
-    for (int ti = rank; ti < ntiles; ti += CL) {
-        const int j0 = ti * BA_KT, nk = min(BA_KT, pos1 + 1 - j0), jl = j0 + lane;
-        for (int c0 = 0; c0 < G; c0 += p.gt) {
+    constexpr int RB = RBT;                        // rows of one key / value head a warp takes together
+    const int nblk = (nrg + RB - 1) / RB;          // row blocks of one head
+    // a round = one tile of keys x one group of `gt` heads; this CTA's rounds in order, the next one's loads always in flight
+    const int ngrp = (G + p.gt - 1) / p.gt;
+    const int nround = rank < ntiles ? ((ntiles - rank + CL - 1) / CL) * ngrp : 0;
+    const size_t bufK = (size_t)p.gt * BA_KT * (dk + 4), bufV = (size_t)p.gt * BA_KT * (dv + 4);
+    auto load_round = [&](int rd) {
+        const int ti = rank + (rd / ngrp) * CL, c0 = (rd % ngrp) * p.gt;
+        const int j0 = ti * BA_KT;
+        ba_load_tiles(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, (size_t)G * dk + (size_t)c0 * dv, dv, sK + (rd & 1) * bufK, tsk,
+                      sV + (rd & 1) * bufV, tsv, min(p.gt, G - c0), min(BA_KT, pos1 + 1 - j0), j0, vec);
+    };
+    if (nround > 0) load_round(0);
+    for (int rd = 0; rd < nround; ++rd) {
+        if (rd + 1 < nround) {
+            load_round(rd + 1);                    // into the buffer that round rd - 1 used: everyone left it at the barrier below
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();                           // round rd's tiles are visible (and, the first time, the rows are initialised)
+        {
+            const int ti = rank + (rd / ngrp) * CL, c0 = (rd % ngrp) * p.gt;
+            const int j0 = ti * BA_KT, nk = min(BA_KT, pos1 + 1 - j0), jl = j0 + lane;
             const int gn = min(p.gt, G - c0);
-            __syncthreads();                       // the tile buffers are free (and the rows are initialised)
-            ba_load_tiles(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, (size_t)G * dk + (size_t)c0 * dv, dv, sK, tsk, sV, tsv, gn, nk, j0, vec);
+            const float* cK = sK + (rd & 1) * bufK;
+            const float* cV = sV + (rd & 1) * bufV;
             for (int it = warp; it < gn * nblk; it += nw) {
-                const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * BA_RB, nr = min(BA_RB, nrg - rr0);
-                int rows[BA_RB];
-                const float* qv[BA_RB];
+                const int cl_ = it / nblk, c = c0 + cl_, rr0 = (it % nblk) * RB, nr = min(RB, nrg - rr0);
+                int rows[RBT];
+                const float* qv[RBT];
 #pragma unroll
-                for (int b = 0; b < BA_RB; ++b) {
+                for (int b = 0; b < RBT; ++b) {
                     const int rr = rr0 + min(b, nr - 1);
                     rows[b] = (rr / rep) * H + c * rep + rr % rep;
                     qv[b] = sQ + (size_t)rows[b] * dk;
                 }
                 // ---- scores of the warp's rows against key `lane` ----
-                float sc[BA_RB] = {0.f, 0.f, 0.f, 0.f};
+                float sc[RBT];
+#pragma unroll
+                for (int b = 0; b < RBT; ++b) sc[b] = 0.f;
                 if (lane < nk) {
-                    const float* kv = sK + ((size_t)cl_ * BA_KT + lane) * tsk;
+                    const float* kv = cK + ((size_t)cl_ * BA_KT + lane) * tsk;
                     if (vec) {
                         const float4* k4 = reinterpret_cast<const float4*>(kv);
 #pragma unroll 4
                         for (int i = 0; i < dk / 4; ++i) {
                             const float4 kx = k4[i];
 #pragma unroll
-                            for (int b = 0; b < BA_RB; ++b) {
+                            for (int b = 0; b < RBT; ++b) {
                                 const float4 qx = reinterpret_cast<const float4*>(qv[b])[i];
                                 sc[b] = fmaf(qx.x, kx.x, sc[b]); sc[b] = fmaf(qx.y, kx.y, sc[b]);
                                 sc[b] = fmaf(qx.z, kx.z, sc[b]); sc[b] = fmaf(qx.w, kx.w, sc[b]);
@@ -199,13 +220,13 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
                         for (int i = 0; i < dk; ++i) {
                             const float kx = kv[i];
 #pragma unroll
-                            for (int b = 0; b < BA_RB; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
+                            for (int b = 0; b < RBT; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
                         }
                     }
                 }
                 // ---- running maximum / sum of every row, the tile's weights ----
 #pragma unroll
-                for (int b = 0; b < BA_RB; ++b) {
+                for (int b = 0; b < RBT; ++b) {
                     if (b >= nr) break;
                     const int r = rows[b], pq = pos0 + r / H, h = r % H;
                     const bool vis = lane < nk && jl <= pq;
@@ -228,28 +249,29 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
                 }
                 __syncwarp();
                 // ---- weights x values ----
-                const float* vt = sV + (size_t)cl_ * BA_KT * tsv;
+                const float* vt = cV + (size_t)cl_ * BA_KT * tsv;
                 for (int d = lane; d < dv; d += 32) {
-                    float acc[BA_RB];
+                    float acc[RBT];
 #pragma unroll
-                    for (int b = 0; b < BA_RB; ++b) acc[b] = sO[(size_t)rows[b] * dv + d] * sScl[rows[b]];
+                    for (int b = 0; b < RBT; ++b) acc[b] = sO[(size_t)rows[b] * dv + d] * sScl[rows[b]];
 #pragma unroll 2
                     for (int kt = 0; kt < BA_KT; kt += 4) {
                         const float v0 = vt[(kt + 0) * tsv + d], v1 = vt[(kt + 1) * tsv + d], v2 = vt[(kt + 2) * tsv + d], v3 = vt[(kt + 3) * tsv + d];
 #pragma unroll
-                        for (int b = 0; b < BA_RB; ++b) {
+                        for (int b = 0; b < RBT; ++b) {
                             const float4 w4 = *reinterpret_cast<const float4*>(sP + rows[b] * BA_KT + kt);
                             acc[b] = fmaf(w4.x, v0, acc[b]); acc[b] = fmaf(w4.y, v1, acc[b]);
                             acc[b] = fmaf(w4.z, v2, acc[b]); acc[b] = fmaf(w4.w, v3, acc[b]);
                         }
                     }
 #pragma unroll
-                    for (int b = 0; b < BA_RB; ++b)
+                    for (int b = 0; b < RBT; ++b)
                         if (b < nr) sO[(size_t)rows[b] * dv + d] = acc[b];
                 }
                 __syncwarp();
             }
         }
+        __syncthreads();                           // everyone is done with round rd's buffers
     }
     // the CTAs' partial results merged in rank order; every CTA finishes its share of the outputs
     cluster.sync();

@@ -264,6 +264,7 @@ struct KxLayer {
     float *hc_in[2] = {nullptr, nullptr}, *hc_out[2] = {nullptr, nullptr}, *hc_mix[2] = {nullptr, nullptr};
     float *proj_b = nullptr, *rel_bias = nullptr;                // [proj_n], [rel_n + 1][H]
     int rel_n = 0, vmode = 0;
+    int gt_decode = 1;                                           // key / value heads per tile load in decode-shaped steps
     float lam = 0.f;
     // per-sequence memory of fixed size, in the order of the flat state record
     struct Block { float* base; size_t per_slot; };

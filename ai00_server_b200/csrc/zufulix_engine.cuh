@@ -5,6 +5,18 @@
 
 using namespace b200;
 
+// rows of one key / value head a warp of the attention kernel takes together: as many (of 4, 2, 1) as still leave a work item
+// for each of 8 warps
+static inline int zf_rows_per_warp(int gt, int G_, int rep_rows) {
+    int rb = BA_RB;
+    while (rb > 1 && std::min(gt, G_) * cdiv(rep_rows, rb) < 8) rb >>= 1;
+    return rb;
+}
+typedef void (*BiasAttnKernel)(const BiasAttnParams);
+static inline BiasAttnKernel zf_attn_kernel(int rb) {
+    return rb >= 4 ? bias_attn_kernel<4> : (rb == 2 ? bias_attn_kernel<2> : bias_attn_kernel<1>);
+}
+
 void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
     SeqModel& m = *kx;
     const int W = m.W, nl = (int)m.cfg.layers.size();
@@ -91,7 +103,7 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
         }
         l.cache_D = G_ * (dk + dv);
         l.cache = (float*)dalloc((size_t)m.npages * m.page * l.cache_D * 4);
-        while (qb > 1 && bias_attn_smem(qb, H_, dk, dv, 1) > 112 * 1024) qb /= 2;
+        while (qb > 1 && bias_attn_smem(qb, H_, dk, dv, 1) > 112 * 1024) qb /= 2;       // two CTAs per SM where the heads allow it
         REQUIRE(bias_attn_smem(1, H_, dk, dv, 1) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
         z.n_pr = std::max(z.n_pr, (size_t)l.proj_n); z.n_q = std::max(z.n_q, (size_t)H_ * dk); z.n_vout = std::max(z.n_vout, (size_t)H_ * dv);
     }
@@ -99,8 +111,11 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
     for (KxLayer& l : m.layers) {                  // as many key / value heads per tile load as fit beside the chunk's rows
         l.wa_gt = l.c.kv_heads;
         while (l.wa_gt > 1 && bias_attn_smem(qb, l.c.heads, l.c.dim, l.c.vdim, l.wa_gt) > 112 * 1024) l.wa_gt = (l.wa_gt + 1) / 2;
+        // decode-shaped steps have few rows and few CTAs: one CTA per SM may take more heads per load
+        l.gt_decode = l.c.kv_heads;
+        while (l.gt_decode > 1 && bias_attn_smem(1, l.c.heads, l.c.dim, l.c.vdim, l.gt_decode) > 160 * 1024) l.gt_decode = (l.gt_decode + 1) / 2;
     }
-    CK(cudaFuncSetAttribute(bias_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    for (int rb = 1; rb <= BA_RB; rb *= 2) CK(cudaFuncSetAttribute(zf_attn_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     // the largest cluster the attention launch may ask for: what the device can co-schedule at this layer's shared memory
     m.max_split = 8;
     m.wa_ctas_prompt = m.wa_ctas_decode = 8;
@@ -111,21 +126,22 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
             cudaLaunchConfig_t cfg;
             memset(&cfg, 0, sizeof(cfg));
             cfg.gridDim = dim3(cl); cfg.blockDim = dim3(BA_THREADS);
-            cfg.dynamicSmemBytes = bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt);
+            cfg.dynamicSmemBytes = std::max(bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt), bias_attn_smem(1, H_, l.c.dim, l.c.vdim, l.gt_decode));
             cudaLaunchAttribute at;
             at.id = cudaLaunchAttributeClusterDimension;
             at.val.clusterDim.x = (unsigned)cl; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
             cfg.attrs = &at; cfg.numAttrs = 1;
             int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, bias_attn_kernel, &cfg) == cudaSuccess && n > 0) break;
+            if (cudaOccupancyMaxActiveClusters(&n, zf_attn_kernel(BA_RB), &cfg) == cudaSuccess && n > 0) break;
             cudaGetLastError();
         }
         m.max_split = std::min(m.max_split, cl);
-        const int thr_p = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), BA_RB) >= 16 ? BA_THREADS : 256;
-        const int thr_d = std::min(l.wa_gt, G_) * cdiv(H_ / G_, BA_RB) >= 16 ? BA_THREADS : 256;
+        const int rb_p = zf_rows_per_warp(l.wa_gt, G_, qb * (H_ / G_)), rb_d = zf_rows_per_warp(l.gt_decode, G_, H_ / G_);
+        const int thr_p = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), rb_p) >= 16 ? BA_THREADS : 256;
+        const int thr_d = std::min(l.gt_decode, G_) * cdiv(H_ / G_, rb_d) >= 16 ? BA_THREADS : 256;
         int np = 1, nd = 1;
-        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&np, bias_attn_kernel, thr_p, bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt)));
-        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nd, bias_attn_kernel, thr_d, bias_attn_smem(1, H_, l.c.dim, l.c.vdim, l.wa_gt)));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&np, zf_attn_kernel(rb_p), thr_p, bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt)));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nd, zf_attn_kernel(rb_d), thr_d, bias_attn_smem(1, H_, l.c.dim, l.c.vdim, l.gt_decode)));
         m.wa_ctas_prompt = std::max(1, std::min(m.wa_ctas_prompt, np));
         m.wa_ctas_decode = std::max(1, std::min(m.wa_ctas_decode, nd));
     }
@@ -164,13 +180,15 @@ void b200rwkv_engine::zf_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
                               m.vfirst, G_ * dv, l.vmode, l.lam, H_, G_, dk, dv, c.scale, m.cfg.eps, mv, m.sm};
         launch_k(bias_attn_prep_kernel, dim3(rows), dim3(128), 0, ap, KC_OTHER, s, prof);
         const int qb = decode ? 1 : m.qb_prompt;
-        BiasAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.rel_bias, l.rel_n, H_, G_, dk, dv, qb, l.wa_gt,
+        const int gt = decode ? l.gt_decode : l.wa_gt;
+        BiasAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.rel_bias, l.rel_n, H_, G_, dk, dv, qb, gt,
                           nsplit, mv, m.sm};
         launch_cluster = nsplit;
-        // 16 warps where every warp finds a work item (four rows of one key / value head), 8 otherwise
-        const int items = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), BA_RB);
-        launch_k(bias_attn_kernel, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(items >= 16 ? BA_THREADS : 256),
-                 bias_attn_smem(qb, H_, dk, dv, l.wa_gt), wp, KC_WKV, s, prof);
+        // 16 warps where every warp finds a work item (some rows of one key / value head), 8 otherwise
+        const int rb = zf_rows_per_warp(gt, G_, qb * (H_ / G_));
+        const int items = std::min(gt, G_) * cdiv(qb * (H_ / G_), rb);
+        launch_k(zf_attn_kernel(rb), dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(items >= 16 ? BA_THREADS : 256),
+                 bias_attn_smem(qb, H_, dk, dv, gt), wp, KC_WKV, s, prof);
         kx_lin(s, prof, lin(m.vout, H_ * dv, l.o, m.y, W, W, H_ * dv), rows, 1);
         pend.mix = l.hc_mix[0]; pend.out = l.hc_out[0]; pend.y = m.y;
         if (c.has_mlp) {

@@ -392,43 +392,100 @@ DG_SIZES = {
 }
 
 
+def _degavik_arm(args, name, time_arm, hbm, tf, peak_kind):
+    """One JSON record: the four-layer Degavik stack (retention + dense, delta rule + experts, windowed attention + experts, delta
+    rule + dense)."""
+    from ai00_server_b200 import runtime, synth
+    B, ctx = args.batch, args.context
+    L = synth.degavik_layer
+    z = DG_SIZES[name]
+    W, V, H, G, dk, dv, E, top, r_ = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["experts"], z["top"], z["low_rank"]
+    moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], shared_ff=z["shared_ff"])
+    dense = dict(mlp="dense", ff=z["dense_ff"])
+    hd = dict(heads=H, dim=dk, vdim=dv)
+    layers = [L("retention", base=1e6, **hd, **dense), L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **moe),
+              L("attention", kv_heads=G, rot_dims=dk // 2, base=5e5, window=z["window"], keep_first=z["keep_first"], softcap=30.0, **hd, **moe),
+              L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **dense)]
+    cfg, st, _ = synth.make_degavik(layers, width=W, vocab=V, seed=1, low_rank=r_, arrays=False)
+    # algorithmic work: weights one token touches, weights a decode step streams (dense + reachable experts), recurrent states
+    # read and written, cache rows inside the window
+    o = W * H * dv
+    mix = {"ret": 2 * H * dk * W + 2 * H * dv * W + o,
+           "delta": 2 * G * dk * W + H * dv * W + H * W + 2 * r_ * W + H * dk * r_ + H * dv * r_ + o,
+           "attn": H * dk * W + G * dk * W + G * dv * W + o}
+    ff_moe, ff_dense, expert = E * W + 3 * W * z["shared_ff"], 3 * W * z["dense_ff"], 3 * W * z["ff"]
+    per_layer = [mix["ret"] + ff_dense, mix["delta"] + ff_moe, mix["attn"] + ff_moe, mix["delta"] + ff_dense]
+    reach = min(E, B * top)
+    active = sum(per_layer) + 2 * top * expert + V * W
+    seen = min(ctx, z["window"] + z["keep_first"])
+    state_bytes = 3 * B * H * dk * dv * 4 * 2                       # three recurrent layers, read + write
+    step_bytes = 2 * (sum(per_layer) + 2 * reach * expert + V * W) + state_bytes + B * seen * G * (dk + dv) * 4
+    attn_flops_tok = 2 * H * (dk + dv) * min(ctx / 2, seen) + 3 * 2 * 2 * H * dk * dv       # scores + values, three state updates
+    m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+    r = time_arm(m, V, m.state.reset)
+    m.close()
+    r.update({"family": "degavik", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+              "decode_algorithmic_bytes_per_step": int(step_bytes),
+              "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+              "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+              "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+              "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+    return r
+
+
 def degavik_main(args):
-    """Prefill and decode throughput of the Degavik family (retention + dense, delta rule + experts, windowed attention + experts,
-    delta rule + dense) beside the closest existing family, a Kemirax stack of equal width, depth and vocabulary."""
+    """Prefill and decode throughput of the Degavik family beside the closest existing family, a Kemirax stack of equal width,
+    depth and vocabulary."""
+    peaks, peak_kind = read_peaks()
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    time_arm = _family_timer(args, np.random.default_rng(7))
+    for name in args.kx_sizes.split(","):
+        print(json.dumps(_degavik_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
+        print(json.dumps(_kemirax_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
+
+
+ZF_SIZES = {
+    # width; heads / key-value heads / head sizes; bias table rows and the distance of its last bucket; residual streams; experts x ff, top,
+    # groups (count, keep); dense ff; vocab.  Width, depth, heads, head sizes and vocabulary are those of DG_SIZES; the feed-forwards have
+    # two matrices instead of three, so their hidden sizes are 3 / 2 of DG_SIZES' for the same number of weights
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, rel_rows=32, bias_max=128, streams=4, experts=8, ff=768, top=2, groups=(4, 2),
+                  dense_ff=4224, vocab=32768),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rel_rows=32, bias_max=128, streams=4, experts=16, ff=1536, top=4, groups=(4, 2),
+                  dense_ff=8448, vocab=32768),
+}
+
+
+def zufulix_main(args):
+    """Prefill and decode throughput of the Zufulix family (four attention layers over the whole context with a distance bias:
+    dense, experts, experts, dense feed-forwards; four residual streams) beside the closest existing family, a Degavik stack of
+    equal width, depth and vocabulary."""
     from ai00_server_b200 import runtime, synth
     peaks, peak_kind = read_peaks()
     hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
     B, ctx = args.batch, args.context
     time_arm = _family_timer(args, np.random.default_rng(7))
-    L = synth.degavik_layer
+    L = synth.zufulix_layer
     for name in args.kx_sizes.split(","):
-        z = DG_SIZES[name]
-        W, V, H, G, dk, dv, E, top, r_ = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["experts"], z["top"], z["low_rank"]
-        moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], shared_ff=z["shared_ff"])
+        z = ZF_SIZES[name]
+        W, V, H, G, dk, dv, E, top = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["experts"], z["top"]
+        att = dict(heads=H, kv_heads=G, dim=dk, vdim=dv, bias_max=z["bias_max"])
+        moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], groups=z["groups"])
         dense = dict(mlp="dense", ff=z["dense_ff"])
-        hd = dict(heads=H, dim=dk, vdim=dv)
-        layers = [L("retention", base=1e6, **hd, **dense), L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **moe),
-                  L("attention", kv_heads=G, rot_dims=dk // 2, base=5e5, window=z["window"], keep_first=z["keep_first"], softcap=30.0, **hd, **moe),
-                  L("channel_delta", kv_heads=G, conv=z["conv"], **hd, **dense)]
-        cfg, st, _ = synth.make_degavik(layers, width=W, vocab=V, seed=1, low_rank=r_, arrays=False)
-        # algorithmic work: weights one token touches, weights a decode step streams (dense + reachable experts), recurrent states
-        # read and written, cache rows inside the window
-        o = W * H * dv
-        mix = {"ret": 2 * H * dk * W + 2 * H * dv * W + o,
-               "delta": 2 * G * dk * W + H * dv * W + H * W + 2 * r_ * W + H * dk * r_ + H * dv * r_ + o,
-               "attn": H * dk * W + G * dk * W + G * dv * W + o}
-        ff_moe, ff_dense, expert = E * W + 3 * W * z["shared_ff"], 3 * W * z["dense_ff"], 3 * W * z["ff"]
-        per_layer = [mix["ret"] + ff_dense, mix["delta"] + ff_moe, mix["attn"] + ff_moe, mix["delta"] + ff_dense]
+        layers = [L(**att, **dense), L(**att, **moe), L(**att, **moe), L(**att, **dense)]
+        cfg, st, _ = synth.make_zufulix(layers, width=W, vocab=V, seed=1, streams=z["streams"], rel_rows=z["rel_rows"], arrays=False)
+        # algorithmic work: weights one token touches, weights a decode step streams (dense + reachable experts; the embedding
+        # table is the output matrix), cache rows of the whole context in every layer
+        mix = H * dk * W + G * dk * W + G * dv * W + W * H * dv
+        ff_moe, ff_dense, expert = E * W, 2 * W * z["dense_ff"], 2 * W * z["ff"]
+        per_layer = [mix + ff_dense, mix + ff_moe, mix + ff_moe, mix + ff_dense]
         reach = min(E, B * top)
         active = sum(per_layer) + 2 * top * expert + V * W
-        seen = min(ctx, z["window"] + z["keep_first"])
-        state_bytes = 3 * B * H * dk * dv * 4 * 2                       # three recurrent layers, read + write
-        step_bytes = 2 * (sum(per_layer) + 2 * reach * expert + V * W) + state_bytes + B * seen * G * (dk + dv) * 4
-        attn_flops_tok = 2 * H * (dk + dv) * min(ctx / 2, seen) + 3 * 2 * 2 * H * dk * dv       # scores + values, three state updates
+        step_bytes = 2 * (sum(per_layer) + 2 * reach * expert + V * W) + 4 * B * ctx * G * (dk + dv) * 4
+        attn_flops_tok = 4 * 2 * H * (dk + dv) * ctx / 2           # scores + values of four layers, mean context ctx / 2 during the prompt
         m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
         r = time_arm(m, V, m.state.reset)
         m.close()
-        r.update({"family": "degavik", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+        r.update({"family": "zufulix", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
                   "decode_algorithmic_bytes_per_step": int(step_bytes),
                   "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
                   "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
@@ -436,7 +493,7 @@ def degavik_main(args):
                   "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
         print(json.dumps(r), flush=True)
         del st
-        print(json.dumps(_kemirax_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
+        print(json.dumps(_degavik_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
 
 
 def main():
@@ -457,19 +514,22 @@ def main():
     ap.add_argument("--quant-layers", type=int, default=-1, help="the reference's `quant`: first N layers (default: all)")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--seq-len", type=int, default=512)
-    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax", "degavik"],
-                    help="kemirax / degavik: prefill and decode throughput of that family at layer sizes of a real model (random weights), "
-                         "beside the closest existing family at equal width and depth (RWKV-7 for kemirax, Kemirax for degavik); one "
+    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax", "degavik", "zufulix"],
+                    help="kemirax / degavik / zufulix: prefill and decode throughput of that family at layer sizes of a real model (random "
+                         "weights), beside the closest existing family at equal width and depth (RWKV-7 for kemirax, Kemirax for degavik, "
+                         "Degavik for zufulix); one "
                          "JSON line per arm (not the headline workload)")
-    ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax / degavik: comma-separated size names")
+    ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax / degavik / zufulix: comma-separated size names")
     ap.add_argument("--context", type=int, default=1024,
-                    help="--family kemirax / degavik: tokens each sequence holds before the timed decode steps")
+                    help="--family kemirax / degavik / zufulix: tokens each sequence holds before the timed decode steps")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.family == "kemirax":
         return kemirax_main(args)
     if args.family == "degavik":
         return degavik_main(args)
+    if args.family == "zufulix":
+        return zufulix_main(args)
     PRESET, BATCH = args.preset, args.batch
     METRIC = metric_name(PRESET, BATCH)
     if args.quant != "none":

@@ -71,14 +71,14 @@ def attention(w, p, c, eps, h, mem, pos, shared):
     mem.setdefault("k", []).append(k)
     mem.setdefault("v", []).append(v)
     rel = w[p + "rel"]
+    K, V = np.stack(mem["k"]), np.stack(mem["v"])      # [pos + 1, G, d]
+    bucket = [distance_bucket(pos - j, rel.shape[0], c["bias_max"]) for j in range(pos + 1)]
     out = np.zeros((H, dv))
     for hh in range(H):
         g = hh // (H // G)
-        s = np.array([q[hh] @ mem["k"][j][g] * c["scale"] + rel[distance_bucket(pos - j, rel.shape[0], c["bias_max"]), hh]
-                      for j in range(pos + 1)])
+        s = K[:, g] @ q[hh] * c["scale"] + rel[bucket, hh]
         e = np.exp(s - s.max())
-        pr = e / e.sum()
-        out[hh] = sum(pr[j] * mem["v"][j][g] for j in range(pos + 1))
+        out[hh] = (e / e.sum()) @ V[:, g]
     return lin(w[p + "o"], out.reshape(-1))
 
 
