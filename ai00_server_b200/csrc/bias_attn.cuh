@@ -19,7 +19,9 @@
 //                           CTAs' partial results are merged through distributed shared memory in rank order.  A warp owns
 //                           1, 2 or 4 rows of one key / value head (template): it scores them against a key per lane, then
 //                           applies the tile's weights to the values, with no CTA barrier in between; the next tiles arrive by
-//                           cp.async into a second buffer meanwhile.  Scores, weights and sums in f32.
+//                           cp.async into a second buffer meanwhile.  Scores, weights and sums in f32.  Any head size.
+//   bias_attn_reg_kernel    the same result for head sizes that are multiples of four up to 128, with nothing staged in shared
+//                           memory: see the comment above it.
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda_runtime.h>
@@ -84,6 +86,7 @@ struct BiasAttnParams {
     int qb;                                       // tokens per chunk the shared memory was sized for
     int gt;                                       // key / value heads per tile load
     int cl;                                       // CTAs per chunk (cluster size)
+    int ks;                                       // register form: warps of a CTA that share one item's key tiles
     MetaView meta; SeqMeta sm;
 };
 
@@ -289,6 +292,225 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
             }
         }
         p.out[(size_t)(t0 + r / H) * p.ldo + (size_t)(r % H) * dv + d] = num / den;
+    }
+    cluster.sync();                                // nobody leaves while its shared memory is still being read
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// register form (head sizes that are multiples of four, at most 128): no tile passes through shared memory
+// ------------------------------------------------------------------------------------------------------------------
+// A warp owns RB rows of one key / value head and a share of the chunk's key tiles, and keeps everything it accumulates in
+// registers: lane l holds entries 4l .. 4l + 3 of the RB query rows and of the RB un-normalised output rows, plus the rows'
+// running maxima and sums.  Per tile of 32 keys:
+//   scores   eight keys at a time: every lane loads its 16 bytes of each key row straight from the cache (a whole row per warp
+//            load), multiplies them with its query entries, and a butterfly over the lanes (keep half of the keys, send the other
+//            half: 4 + 2 + 1 exchanges, then two plain ones) leaves the finished score of key (l >> 2) of the batch in lane l;
+//   softmax  bias, causal mask, running maximum / sum with three exchanges per row;
+//   values   the weight of each key is broadcast from its lane, every lane loads its 16 bytes of the value row.
+// With few (head, row block) items per chunk the key tiles are split over KS warps per item as well as over the cluster's
+// CTAs; the partial (maximum, sum, output) triples meet in shared memory (within a CTA) and then through distributed shared
+// memory (across the cluster), always in a fixed order.
+constexpr int BAR_THREADS = 256;                   // 8 warps, two CTAs per SM (128 registers per thread)
+
+__host__ __device__ inline size_t bias_attn_reg_smem(int qb, int H, int G, int dv, int rb, int ks) {
+    const size_t nblk = ((size_t)qb * (H / G) + rb - 1) / rb, slots = (size_t)G * nblk * ks;
+    return (slots * rb * (dv + 2) + 2 * (size_t)G * nblk * rb + 8) * sizeof(float);
+}
+
+template <int RB>
+__global__ void __launch_bounds__(BAR_THREADS, 2) bias_attn_reg_kernel(const BiasAttnParams p) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = p.cl, rank = blockIdx.x % CL, ch = blockIdx.x / CL;
+    if (ch >= p.sm.n_chunks()) return;             // the same for every CTA of a cluster
+    const int t0 = p.sm.chunk_start()[ch], nq = p.sm.chunk_count()[ch];
+    const int slot = p.meta.tok_slot()[t0];
+    const int pos0 = p.sm.tok_pos()[t0], pos1 = pos0 + nq - 1;
+    const int H = p.H, G = p.G, dk = p.dk, dv = p.dv, rep = H / G, R = nq * H, KS = p.ks;
+    const int D = G * (dk + dv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, NW = blockDim.x >> 5;
+    const int nblk_cap = (p.qb * rep + RB - 1) / RB;          // row blocks of one head the shared memory was sized for
+    const int nrg = nq * rep, nblk = (nrg + RB - 1) / RB;     // rows / row blocks of one head in this chunk
+    extern __shared__ __align__(16) float bar_smem[];
+    float* sO = bar_smem;                                      // [G * nblk_cap][KS][RB][dv] partial outputs (slot 0 of an item: merged)
+    float* sM = sO + (size_t)G * nblk_cap * KS * RB * dv;      // [G * nblk_cap][KS][RB]
+    float* sL = sM + (size_t)G * nblk_cap * KS * RB;
+    float* sM2 = sL + (size_t)G * nblk_cap * KS * RB;          // [G * nblk_cap][RB] merged over the CTA's key splits
+    float* sL2 = sM2 + (size_t)G * nblk_cap * RB;
+    const int* tbl = p.table + (size_t)slot * p.stride;
+    const int ntiles = (pos1 + BA_KT) / BA_KT;                 // keys 0 .. pos1
+    const int l4 = lane * 4, kq = lane >> 2;
+    const bool kact = l4 < dk, vact = l4 < dv;
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int it = warp; it < G * nblk * KS; it += NW) {
+        const int item = it / KS, ks = it % KS;
+        const int c = item / nblk, rr0 = (item % nblk) * RB, nr = min(RB, nrg - rr0);
+        int qi[RB], hh[RB];
+        float4 q[RB], acc[RB];
+        float m[RB], l[RB];
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            const int rr = rr0 + min(b, nr - 1);
+            qi[b] = rr / rep; hh[b] = c * rep + rr % rep;
+            q[b] = kact ? *reinterpret_cast<const float4*>(p.q + (size_t)(t0 + qi[b]) * p.ldq + (size_t)hh[b] * dk + l4) : zero4;
+            acc[b] = zero4; m[b] = -CUDART_INF_F; l[b] = 0.f;
+        }
+        const float* kbase = p.cache + (size_t)c * dk + l4;
+        const float* vbase = p.cache + (size_t)G * dk + (size_t)c * dv + l4;
+        for (int ti = rank * KS + ks; ti < ntiles; ti += CL * KS) {
+            const int j0 = ti * BA_KT, nk = min(BA_KT, pos1 + 1 - j0);
+            unsigned long long myoff = 0ull;                   // cache offset of key j0 + lane
+            if (lane < nk) {
+                const int j = j0 + lane, pg = j / p.page;
+                myoff = ((unsigned long long)tbl[pg] * p.page + (unsigned)(j - pg * p.page)) * (unsigned)D;
+            }
+            float s[4][RB];
+            // ---- scores: four batches of eight keys ----
+#pragma unroll
+            for (int bt = 0; bt < 4; ++bt) {
+                float4 kx[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const unsigned long long off = __shfl_sync(0xffffffffu, myoff, bt * 8 + u);
+                    kx[u] = (kact && bt * 8 + u < nk) ? __ldg(reinterpret_cast<const float4*>(kbase + off)) : zero4;
+                }
+#pragma unroll
+                for (int b = 0; b < RB; ++b) {
+                    float pt[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        pt[u] = fmaf(q[b].x, kx[u].x, fmaf(q[b].y, kx[u].y, fmaf(q[b].z, kx[u].z, q[b].w * kx[u].w)));
+                    // butterfly: lanes with bit 4 set keep keys 4..7 and send 0..3, and so on; lane l ends with key (l >> 2) & 7
+                    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+                    float a4[4], a2[2], a1;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float send = h16 ? pt[i] : pt[i + 4], keep = h16 ? pt[i + 4] : pt[i];
+                        a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const float send = h8 ? a4[i] : a4[i + 2], keep = h8 ? a4[i + 2] : a4[i];
+                        a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                    }
+                    {
+                        const float send = h4 ? a2[0] : a2[1], keep = h4 ? a2[1] : a2[0];
+                        a1 = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+                    }
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+                    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+                    s[bt][b] = a1;
+                }
+            }
+            // ---- bias, causal mask, running maximum and sum of every row; s becomes the tile's weights ----
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+                const int pq = pos0 + qi[b];
+                float tmax = -CUDART_INF_F;
+#pragma unroll
+                for (int bt = 0; bt < 4; ++bt) {
+                    const int kk = bt * 8 + kq, j = j0 + kk;
+                    const bool vis = kk < nk && j <= pq;
+                    s[bt][b] = vis ? s[bt][b] + p.bias[(size_t)min(pq - j, p.nb) * H + hh[b]] : -CUDART_INF_F;
+                    tmax = fmaxf(tmax, s[bt][b]);
+                }
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 16));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 8));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 4));
+                const float mn = fmaxf(m[b], tmax);            // the same in every lane
+                const bool any = mn > -CUDART_INF_F;
+                const float scl = (any && m[b] > -CUDART_INF_F) ? expf(m[b] - mn) : 0.f;
+                float tsum = 0.f;
+#pragma unroll
+                for (int bt = 0; bt < 4; ++bt) {
+                    const float w = (any && s[bt][b] > -CUDART_INF_F) ? expf(s[bt][b] - mn) : 0.f;
+                    s[bt][b] = w;
+                    tsum += w;
+                }
+                tsum += __shfl_xor_sync(0xffffffffu, tsum, 16);
+                tsum += __shfl_xor_sync(0xffffffffu, tsum, 8);
+                tsum += __shfl_xor_sync(0xffffffffu, tsum, 4);   // lanes that differ in bits 0..1 hold the same keys
+                l[b] = l[b] * scl + tsum;
+                m[b] = mn;
+                acc[b].x *= scl; acc[b].y *= scl; acc[b].z *= scl; acc[b].w *= scl;
+            }
+            // ---- weights x values ----
+#pragma unroll
+            for (int bt = 0; bt < 4; ++bt) {
+                if (bt * 8 >= nk) break;                       // warp-uniform
+                float4 vx[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const unsigned long long off = __shfl_sync(0xffffffffu, myoff, bt * 8 + u);
+                    vx[u] = (vact && bt * 8 + u < nk) ? __ldg(reinterpret_cast<const float4*>(vbase + off)) : zero4;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int b = 0; b < RB; ++b) {
+                        const float w = __shfl_sync(0xffffffffu, s[bt][b], u << 2);
+                        acc[b].x = fmaf(w, vx[u].x, acc[b].x); acc[b].y = fmaf(w, vx[u].y, acc[b].y);
+                        acc[b].z = fmaf(w, vx[u].z, acc[b].z); acc[b].w = fmaf(w, vx[u].w, acc[b].w);
+                    }
+            }
+        }
+        const size_t sl = (size_t)(c * nblk_cap + item % nblk) * KS + ks;
+#pragma unroll
+        for (int b = 0; b < RB; ++b) {
+            if (b >= nr) break;
+            if (vact) *reinterpret_cast<float4*>(sO + (sl * RB + b) * dv + l4) = acc[b];
+            if (lane == 0) { sM[sl * RB + b] = m[b]; sL[sl * RB + b] = l[b]; }
+        }
+    }
+    __syncthreads();
+    // the CTA's key splits of every row merged in split order (into split 0's place)
+    for (int e = threadIdx.x; e < R * dv; e += (int)blockDim.x) {
+        const int r = e / dv, d = e % dv, qi_ = r / H, h = r % H, c = h / rep, rr = qi_ * rep + h % rep;
+        const size_t it0 = (size_t)(c * nblk_cap + rr / RB) * KS;
+        const int b = rr % RB;
+        float mx = -CUDART_INF_F;
+        for (int k = 0; k < KS; ++k) mx = fmaxf(mx, sM[(it0 + k) * RB + b]);
+        float num = 0.f, den = 0.f;
+        for (int k = 0; k < KS; ++k) {
+            const float mr = sM[(it0 + k) * RB + b];
+            if (mr > -CUDART_INF_F) {
+                const float f = expf(mr - mx);
+                num = fmaf(sO[((it0 + k) * RB + b) * dv + d], f, num);
+                den = fmaf(sL[(it0 + k) * RB + b], f, den);
+            }
+        }
+        sO[(it0 * RB + b) * dv + d] = num;                     // only this thread touches column d of the row
+        if (d == 0) { sM2[(it0 / KS) * RB + b] = mx; sL2[(it0 / KS) * RB + b] = den; }
+    }
+    // the CTAs' partial results merged in rank order; every CTA finishes its share of the outputs
+    cluster.sync();
+    for (int e = rank * (int)blockDim.x + threadIdx.x; e < R * dv; e += CL * (int)blockDim.x) {
+        const int r = e / dv, d = e % dv, qi_ = r / H, h = r % H, c = h / rep, rr = qi_ * rep + h % rep;
+        const size_t ib = (size_t)(c * nblk_cap + rr / RB);
+        const int b = rr % RB;
+        // all remote reads first (a cluster has at most 8 CTAs), then the arithmetic: the reads overlap instead of queueing up
+        float mr[8], orr[8], lr[8];
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk) {
+            mr[rk] = -CUDART_INF_F; orr[rk] = 0.f; lr[rk] = 0.f;
+            if (rk < CL) {
+                mr[rk] = cluster.map_shared_rank(sM2, rk)[ib * RB + b];
+                orr[rk] = cluster.map_shared_rank(sO, rk)[(ib * KS * RB + b) * dv + d];
+                lr[rk] = cluster.map_shared_rank(sL2, rk)[ib * RB + b];
+            }
+        }
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk) mx = fmaxf(mx, mr[rk]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk)
+            if (mr[rk] > -CUDART_INF_F) {
+                const float f = expf(mr[rk] - mx);
+                num = fmaf(orr[rk], f, num);
+                den = fmaf(lr[rk], f, den);
+            }
+        p.out[(size_t)(t0 + qi_) * p.ldo + (size_t)h * dv + d] = num / den;
     }
     cluster.sync();                                // nobody leaves while its shared memory is still being read
 }

@@ -19,7 +19,7 @@
 
 namespace b200 {
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 16;                // kernel template: loops unrolled for up to 4, 8 or 16 streams
 constexpr int HC_MAX_TOP = 8;
 
 enum HcRead { HC_READ_NONE = 0, HC_READ_MIX = 1, HC_READ_SUM = 2 };
@@ -44,15 +44,18 @@ struct HcStepParams {
     MetaView meta;
 };
 
-__global__ void __launch_bounds__(NORM_THREADS) hc_step_kernel(const HcStepParams p) {
+constexpr int HC_THREADS_FEW_ROWS = 1024;       // block size for steps of few tokens (decode): a thread then owns one or two columns
+
+template <int THREADS, int SMAX>
+__global__ void __launch_bounds__(THREADS) hc_step_kernel(const HcStepParams p) {
     __shared__ float red[32];
-    __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_out[HC_MAX_STREAMS], s_in[HC_MAX_STREAMS];
+    __shared__ float s_mix[SMAX * SMAX], s_out[SMAX], s_in[SMAX];
     extern __shared__ __align__(16) float hc_u[];      // [W] the read row
     const int t = blockIdx.x;
     if (t >= p.meta.T()) return;
     const int S = p.S, W = p.W;
     const bool upd = p.upd_out != nullptr;
-    if (threadIdx.x < S * S && upd) s_mix[threadIdx.x] = p.upd_mix[threadIdx.x];
+    for (int i = threadIdx.x; i < S * S && upd; i += blockDim.x) s_mix[i] = p.upd_mix[i];
     if (threadIdx.x < S) {
         if (upd) s_out[threadIdx.x] = p.upd_out[threadIdx.x];
         s_in[threadIdx.x] = p.read == HC_READ_MIX ? p.rd_in[threadIdx.x] : 1.f;
@@ -64,12 +67,16 @@ __global__ void __launch_bounds__(NORM_THREADS) hc_step_kernel(const HcStepParam
             if (k < p.top) { rw[k] = p.row_of[(size_t)t * p.top + k]; wg[k] = p.wgt[(size_t)t * p.top + k]; }
     }
     __syncthreads();
-    float* xt = p.x + (size_t)t * S * W;
+    // a column of the token's streams is read and written by one thread only, and nothing else the loop reads is written here
+    float* __restrict__ xt = p.x + (size_t)t * S * W;
+    const float* __restrict__ yrow = p.y ? p.y + (size_t)t * W : nullptr;
+    const float* __restrict__ erows = p.rows;
     float sum = 0.f;
+#pragma unroll 2
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float xs[HC_MAX_STREAMS];
+        float xs[SMAX];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+        for (int s = 0; s < SMAX; ++s)
             if (s < S) xs[s] = xt[(size_t)s * W + c];
         if (upd) {
             float yv;
@@ -77,28 +84,28 @@ __global__ void __launch_bounds__(NORM_THREADS) hc_step_kernel(const HcStepParam
                 yv = 0.f;
 #pragma unroll
                 for (int k = 0; k < HC_MAX_TOP; ++k)
-                    if (k < p.top) yv = fmaf(wg[k], p.rows[(size_t)rw[k] * W + c], yv);
+                    if (k < p.top) yv = fmaf(wg[k], erows[(size_t)rw[k] * W + c], yv);
             } else {
-                yv = p.y[(size_t)t * W + c];
+                yv = yrow[c];
             }
-            float xn[HC_MAX_STREAMS];
+            float xn[SMAX];
 #pragma unroll
-            for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+            for (int to = 0; to < SMAX; ++to) {
                 if (to >= S) break;
                 float a = 0.f;
 #pragma unroll
-                for (int fr = 0; fr < HC_MAX_STREAMS; ++fr)
+                for (int fr = 0; fr < SMAX; ++fr)
                     if (fr < S) a = fmaf(s_mix[fr * S + to], xs[fr], a);
                 xn[to] = fmaf(s_out[to], yv, a);
             }
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < SMAX; ++s)
                 if (s < S) { xs[s] = xn[s]; xt[(size_t)s * W + c] = xn[s]; }
         }
         if (p.read != HC_READ_NONE) {
             float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < SMAX; ++s)
                 if (s < S) u = fmaf(s_in[s], xs[s], u);
             hc_u[c] = u;
             sum += u;

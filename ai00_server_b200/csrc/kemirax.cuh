@@ -265,6 +265,7 @@ struct KxLayer {
     float *proj_b = nullptr, *rel_bias = nullptr;                // [proj_n], [rel_n + 1][H]
     int rel_n = 0, vmode = 0;
     int gt_decode = 1;                                           // key / value heads per tile load in decode-shaped steps
+    bool attn_reg = false;                                       // head sizes fit the attention kernel's register form
     float lam = 0.f;
     // per-sequence memory of fixed size, in the order of the flat state record
     struct Block { float* base; size_t per_slot; };
@@ -291,6 +292,8 @@ struct SeqModel {
     float* vfirst = nullptr;                      // [T, G * dv] values of the first blending attention layer, this step's tokens
     int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
     int wa_ctas_prompt = 1, wa_ctas_decode = 1;   // windowed-attention CTAs one SM holds at once (prompt / decode shape)
+    int cl_cap_prompt[4] = {1 << 30, 1 << 30, 1 << 30, 1 << 30};   // clusters of 1 / 2 / 4 / 8 attention CTAs the GPU holds at once, where a
+    int cl_cap_decode[4] = {1 << 30, 1 << 30, 1 << 30, 1 << 30};   // family's loader has asked the device (a launch should stay within one wave)
     float *y = nullptr, *cv = nullptr, *gl = nullptr;   // sublayer output, convolution output, output-gate logits
     __nv_bfloat16 *embed = nullptr, *head = nullptr;
     // sequence memory

@@ -20,7 +20,7 @@ static KxConfig zf_parse_config(const JVal& root) {
     if (root.has("embedding") && root.at("embedding").has("scale")) c.embed_scale = (float)root.at("embedding").number("scale");
     if (root.has("streams")) {
         c.streams = root.integer("streams");
-        REQUIRE(c.streams >= 1 && c.streams <= HC_MAX_STREAMS, B200RWKV_ERR_UNSUPPORTED, "config: streams must be in 1..8");
+        REQUIRE(c.streams >= 1 && c.streams <= HC_MAX_STREAMS, B200RWKV_ERR_UNSUPPORTED, "config: streams must be in 1..16");
     }
     const JVal& ls = root.at("layers");
     REQUIRE(ls.kind == JVal::ARR && !ls.arr.empty(), B200RWKV_ERR_INVALID, "config: layers");

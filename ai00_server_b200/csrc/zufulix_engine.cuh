@@ -16,6 +16,39 @@ typedef void (*BiasAttnKernel)(const BiasAttnParams);
 static inline BiasAttnKernel zf_attn_kernel(int rb) {
     return rb >= 4 ? bias_attn_kernel<4> : (rb == 2 ? bias_attn_kernel<2> : bias_attn_kernel<1>);
 }
+static inline BiasAttnKernel zf_attn_reg_kernel(int rb) {
+    return rb >= 4 ? bias_attn_reg_kernel<4> : (rb == 2 ? bias_attn_reg_kernel<2> : bias_attn_reg_kernel<1>);
+}
+
+// the stream kernel unrolled for up to 4, 8 or 16 streams, with large blocks for steps of few tokens
+typedef void (*HcStepKernel)(const HcStepParams);
+static inline HcStepKernel zf_hc_kernel(bool few, int ns) {
+    if (few) return ns <= 4 ? hc_step_kernel<HC_THREADS_FEW_ROWS, 4> : (ns <= 8 ? hc_step_kernel<HC_THREADS_FEW_ROWS, 8> : hc_step_kernel<HC_THREADS_FEW_ROWS, HC_MAX_STREAMS>);
+    return ns <= 4 ? hc_step_kernel<NORM_THREADS, 4> : (ns <= 8 ? hc_step_kernel<NORM_THREADS, 8> : hc_step_kernel<NORM_THREADS, HC_MAX_STREAMS>);
+}
+
+// how one attention launch of a layer runs: which kernel, its block size and shared memory, and the tile / split parameters
+struct ZfAttnPlan { BiasAttnKernel kern; int threads; size_t smem; int gt, ks; };
+
+static ZfAttnPlan zf_attn_plan(const KxLayer& l, int qb_prompt, bool decode) {
+    const int H_ = l.c.heads, G_ = l.c.kv_heads, dk = l.c.dim, dv = l.c.vdim, qb = decode ? 1 : qb_prompt;
+    const int rows = qb * (H_ / G_);               // rows of one key / value head in a full chunk
+    ZfAttnPlan a;
+    if (l.attn_reg) {
+        const int rb = rows >= 4 ? 4 : (rows >= 2 ? 2 : 1);
+        const int items = G_ * cdiv(rows, rb);
+        int ks = 1;                                // few items (decode): the 8 warps share each item's key tiles
+        while (ks < 8 && items * ks * 2 <= BAR_THREADS / 32) ks *= 2;
+        a.kern = zf_attn_reg_kernel(rb); a.threads = BAR_THREADS; a.smem = bias_attn_reg_smem(qb, H_, G_, dv, rb, ks); a.gt = 1; a.ks = ks;
+        return a;
+    }
+    const int gt = decode ? l.gt_decode : l.wa_gt;
+    const int rb = zf_rows_per_warp(gt, G_, rows);
+    // 16 warps where every warp finds a work item (some rows of one key / value head), 8 otherwise
+    a.kern = zf_attn_kernel(rb); a.threads = std::min(gt, G_) * cdiv(rows, rb) >= 16 ? BA_THREADS : 256;
+    a.smem = bias_attn_smem(qb, H_, dk, dv, gt); a.gt = gt; a.ks = 1;
+    return a;
+}
 
 void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
     SeqModel& m = *kx;
@@ -103,8 +136,14 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
         }
         l.cache_D = G_ * (dk + dv);
         l.cache = (float*)dalloc((size_t)m.npages * m.page * l.cache_D * 4);
-        while (qb > 1 && bias_attn_smem(qb, H_, dk, dv, 1) > 112 * 1024) qb /= 2;       // two CTAs per SM where the heads allow it
-        REQUIRE(bias_attn_smem(1, H_, dk, dv, 1) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
+        l.attn_reg = dk % 4 == 0 && dv % 4 == 0 && dk <= 128 && dv <= 128;       // the register form of the attention kernel
+        if (l.attn_reg) {
+            while (qb > 1 && bias_attn_reg_smem(qb, H_, G_, dv, 4, 1) > 160 * 1024) qb /= 2;
+            REQUIRE(bias_attn_reg_smem(1, H_, G_, dv, 4, 8) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "too many attention heads for shared memory");
+        } else {
+            while (qb > 1 && bias_attn_smem(qb, H_, dk, dv, 1) > 112 * 1024) qb /= 2;   // two CTAs per SM where the heads allow it
+            REQUIRE(bias_attn_smem(1, H_, dk, dv, 1) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
+        }
         z.n_pr = std::max(z.n_pr, (size_t)l.proj_n); z.n_q = std::max(z.n_q, (size_t)H_ * dk); z.n_vout = std::max(z.n_vout, (size_t)H_ * dv);
     }
     m.qb_prompt = qb;
@@ -115,38 +154,47 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
         l.gt_decode = l.c.kv_heads;
         while (l.gt_decode > 1 && bias_attn_smem(1, l.c.heads, l.c.dim, l.c.vdim, l.gt_decode) > 160 * 1024) l.gt_decode = (l.gt_decode + 1) / 2;
     }
-    for (int rb = 1; rb <= BA_RB; rb *= 2) CK(cudaFuncSetAttribute(zf_attn_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    for (int rb = 1; rb <= BA_RB; rb *= 2) {
+        CK(cudaFuncSetAttribute(zf_attn_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        CK(cudaFuncSetAttribute(zf_attn_reg_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
     // the largest cluster the attention launch may ask for: what the device can co-schedule at this layer's shared memory
     m.max_split = 8;
     m.wa_ctas_prompt = m.wa_ctas_decode = 8;
     for (const KxLayer& l : m.layers) {
-        const int H_ = l.c.heads, G_ = l.c.kv_heads;
-        int cl = 8;
+        const ZfAttnPlan pp = zf_attn_plan(l, qb, false), pd = zf_attn_plan(l, qb, true);
+        int cl = 8, cl_ok = 0;
         for (; cl > 1; cl >>= 1) {
-            cudaLaunchConfig_t cfg;
-            memset(&cfg, 0, sizeof(cfg));
-            cfg.gridDim = dim3(cl); cfg.blockDim = dim3(BA_THREADS);
-            cfg.dynamicSmemBytes = std::max(bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt), bias_attn_smem(1, H_, l.c.dim, l.c.vdim, l.gt_decode));
-            cudaLaunchAttribute at;
-            at.id = cudaLaunchAttributeClusterDimension;
-            at.val.clusterDim.x = (unsigned)cl; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-            cfg.attrs = &at; cfg.numAttrs = 1;
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, zf_attn_kernel(BA_RB), &cfg) == cudaSuccess && n > 0) break;
-            cudaGetLastError();
+            bool ok = true;
+            for (const ZfAttnPlan* a : {&pp, &pd}) {
+                int lg = 0;
+                while ((1 << lg) < cl) ++lg;
+                cudaLaunchConfig_t cfg;
+                memset(&cfg, 0, sizeof(cfg));
+                cfg.gridDim = dim3(cl); cfg.blockDim = dim3(a->threads);
+                cfg.dynamicSmemBytes = a->smem;
+                cudaLaunchAttribute at;
+                at.id = cudaLaunchAttributeClusterDimension;
+                at.val.clusterDim.x = (unsigned)cl; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+                cfg.attrs = &at; cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, a->kern, &cfg) != cudaSuccess || n <= 0) { ok = false; n = 0; }
+                cudaGetLastError();
+                int& cap = (a == &pd ? m.cl_cap_decode : m.cl_cap_prompt)[lg];      // clusters of this size the GPU holds at once
+                cap = std::min(cap, n);
+            }
+            if (ok && cl_ok == 0) cl_ok = cl;
         }
-        m.max_split = std::min(m.max_split, cl);
-        const int rb_p = zf_rows_per_warp(l.wa_gt, G_, qb * (H_ / G_)), rb_d = zf_rows_per_warp(l.gt_decode, G_, H_ / G_);
-        const int thr_p = std::min(l.wa_gt, G_) * cdiv(qb * (H_ / G_), rb_p) >= 16 ? BA_THREADS : 256;
-        const int thr_d = std::min(l.gt_decode, G_) * cdiv(H_ / G_, rb_d) >= 16 ? BA_THREADS : 256;
+        m.max_split = std::min(m.max_split, std::max(cl_ok, 1));
         int np = 1, nd = 1;
-        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&np, zf_attn_kernel(rb_p), thr_p, bias_attn_smem(qb, H_, l.c.dim, l.c.vdim, l.wa_gt)));
-        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nd, zf_attn_kernel(rb_d), thr_d, bias_attn_smem(1, H_, l.c.dim, l.c.vdim, l.gt_decode)));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&np, pp.kern, pp.threads, pp.smem));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nd, pd.kern, pd.threads, pd.smem));
         m.wa_ctas_prompt = std::max(1, std::min(m.wa_ctas_prompt, np));
         m.wa_ctas_decode = std::max(1, std::min(m.wa_ctas_decode, nd));
     }
     REQUIRE((size_t)W * 4 <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "width too large for the stream kernel");
-    CK(cudaFuncSetAttribute(hc_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    for (int few = 0; few < 2; ++few)
+        for (int ns : {4, 8, HC_MAX_STREAMS}) CK(cudaFuncSetAttribute(zf_hc_kernel(few != 0, ns), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 }
 
 // the whole stack and the last norm: every sublayer boundary is one hc_step launch (write the finished sublayer's output into the
@@ -167,7 +215,8 @@ void b200rwkv_engine::zf_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
     auto boundary = [&](int read, const float* rd_in, const float* ln_w, const float* ln_b, float* h, int compact, float* hidden) {
         HcStepParams hp{m.x, NS, W, pend.mix, pend.out, pend.y, pend.rows, m.row_of, m.wgt, pend.top, read, rd_in, ln_w, ln_b, m.cfg.eps,
                         h, compact, hidden, mv};
-        launch_k(hc_step_kernel, dim3(rows), dim3(NORM_THREADS), (size_t)W * 4, hp, KC_LN, s, prof);
+        const bool few = rows <= 32;
+        launch_k(zf_hc_kernel(few, NS), dim3(rows), dim3(few ? HC_THREADS_FEW_ROWS : NORM_THREADS), (size_t)W * 4, hp, KC_LN, s, prof);
         pend = Pending();
     };
     for (size_t li = 0; li < m.layers.size(); ++li) {
@@ -180,15 +229,11 @@ void b200rwkv_engine::zf_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
                               m.vfirst, G_ * dv, l.vmode, l.lam, H_, G_, dk, dv, c.scale, m.cfg.eps, mv, m.sm};
         launch_k(bias_attn_prep_kernel, dim3(rows), dim3(128), 0, ap, KC_OTHER, s, prof);
         const int qb = decode ? 1 : m.qb_prompt;
-        const int gt = decode ? l.gt_decode : l.wa_gt;
-        BiasAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.rel_bias, l.rel_n, H_, G_, dk, dv, qb, gt,
-                          nsplit, mv, m.sm};
+        const ZfAttnPlan ap_ = zf_attn_plan(l, m.qb_prompt, decode);
+        BiasAttnParams wp{m.q, H_ * dk, l.cache, m.d_table, m.npages, m.page, m.vout, H_ * dv, l.rel_bias, l.rel_n, H_, G_, dk, dv, qb, ap_.gt,
+                          nsplit, ap_.ks, mv, m.sm};
         launch_cluster = nsplit;
-        // 16 warps where every warp finds a work item (some rows of one key / value head), 8 otherwise
-        const int rb = zf_rows_per_warp(gt, G_, qb * (H_ / G_));
-        const int items = std::min(gt, G_) * cdiv(qb * (H_ / G_), rb);
-        launch_k(zf_attn_kernel(rb), dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(items >= 16 ? BA_THREADS : 256),
-                 bias_attn_smem(qb, H_, dk, dv, gt), wp, KC_WKV, s, prof);
+        launch_k(ap_.kern, dim3((decode ? rows : cdiv(rows, qb) + nslot_grid) * nsplit), dim3(ap_.threads), ap_.smem, wp, KC_WKV, s, prof);
         kx_lin(s, prof, lin(m.vout, H_ * dv, l.o, m.y, W, W, H_ * dv), rows, 1);
         pend.mix = l.hc_mix[0]; pend.out = l.hc_out[0]; pend.y = m.y;
         if (c.has_mlp) {

@@ -102,8 +102,9 @@ typedef struct {
     int32_t quant_type;               /* B200RWKV_QUANT_* */
     /* Model families that are described by a config.json beside the weights (architecture "Kemirax": parallel blocks of latent
      * attention / gated linear attention + routed experts; architecture "Degavik": blocks normed on the sublayer outputs with
-     * retention / gated delta rule / windowed attention mixers and dense or routed feed-forwards; bf16 weights): the JSON text,
-     * borrowed during the call.  NULL: the
+     * retention / gated delta rule / windowed attention mixers and dense or routed feed-forwards; architecture "Zufulix": pre-norm
+     * blocks around several copies of the residual with distance-biased attention and dense or group-routed feed-forwards; bf16
+     * weights): the JSON text, borrowed during the call.  NULL: the
      * family is recognised from the tensor names (RWKV v5 / v6 / v7).  Such models keep an attention cache in pages of
      * `kv_page` tokens (0 = 64) drawn from a pool sized for `kv_tokens` tokens over all live sequences (0 = 4096 per slot);
      * precision 0 = bf16 tensor-core products with f32 accumulation, 1 = every product in plain f32.  Their steps hold up to

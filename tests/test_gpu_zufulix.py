@@ -95,12 +95,13 @@ def stack_ref(stack):
     ([L(mlp=None)], {"streams": None, "embed_scale": None}),
     ([L(mlp="dense")], {"streams": 1}),
     ([L(mlp="dense")], {"streams": 8}),
+    ([L(mlp="moe", top=3)], {"streams": 16}),
     ([L(mlp="moe")], {}),
     ([L(mlp="moe", experts=6, top=6, groups=None)], {}),
     ([L(mlp="moe", experts=4, top=1, groups=(4, 2))], {}),
     ([L(kv_heads=2, v_mix=False, mlp=None), L(kv_heads=2, mlp=None), L(kv_heads=2, mlp="dense"), L(kv_heads=2, v_mix=None, mlp=None),
       L(kv_heads=2, heads=8, dim=8, mlp=None)], {}),
-], ids=["attention", "attention-one-kv-head-odd-table", "plain-residual-unscaled-embedding", "one-stream", "eight-streams", "experts-in-groups",
+], ids=["attention", "attention-one-kv-head-odd-table", "plain-residual-unscaled-embedding", "one-stream", "eight-streams", "sixteen-streams", "experts-in-groups",
         "experts-all-chosen-no-groups", "groups-of-one-expert", "value-blend-first-layer-not-layer-0"])
 def test_single_mechanisms(layers, kw):
     b = Bundle(layers, seed=3, **kw)
@@ -322,6 +323,24 @@ def test_wider_layers(precision):
             assert err(got, want) <= TIGHT
         else:
             assert_serving(got, want, bf16_floor(b, toks, want))
+    finally:
+        b.close()
+
+
+# head sizes and head ratios around the attention kernel's two forms (registers: multiples of four up to 128; tiles in shared
+# memory: everything else), with 1 to 8 query heads per key / value head, in prompts of several chunks and in decoding
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(1, 1, 4, 4), (2, 2, 128, 128), (3, 1, 12, 100), (5, 1, 64, 8), (8, 1, 32, 32), (12, 4, 20, 24),
+                                                     (6, 3, 136, 16), (2, 1, 16, 132), (7, 7, 9, 6), (4, 2, 30, 34)])
+def test_head_shapes(heads, kv_heads, dim, vdim):
+    layers = [L(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, bias_max=50, mlp=None),
+              L(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, bias_max=13, mlp="dense")]
+    b = Bundle(layers, seed=heads + dim, width=40, vocab=50, rel_rows=10, kv_page=8)
+    try:
+        toks = b.tokens(100, 2)
+        want = b.oracle(toks)
+        assert err(b.feed(0, toks), want) <= TIGHT
+        out = [b.feed(1, toks[:41])] + [b.feed(1, [t], capi.OPTION_LAST) for t in toks[41:80]] + [b.feed(1, toks[80:83]), b.feed(1, toks[83:])]
+        assert err(np.concatenate(out), want) <= TIGHT
     finally:
         b.close()
 
