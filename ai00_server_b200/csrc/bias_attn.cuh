@@ -148,8 +148,8 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
     const int Rcap = p.qb * H;
     float* sP = ba_smem;                           // [R][KT] weights of the tile (rows start on 16 bytes for any head size)
     float* sK = sP + (size_t)Rcap * BA_KT;         // [2][gt][KT][tsk]
-    float* sV = sK + 2 * (size_t)p.gt * BA_KT * (dk + 4);   // [gt][KT][tsv], two buffers each: a round's tiles arrive while the
-    float* sQ = sV + 2 * (size_t)p.gt * BA_KT * (dv + 4);   // [R][dk]                 previous round is multiplied
+    float* sV = sK + 2 * (size_t)p.gt * BA_KT * (dk + 4);   // [gt][KT][tsv], two buffers each: a stage's tiles arrive while the
+    float* sQ = sV + 2 * (size_t)p.gt * BA_KT * (dv + 4);   // [R][dk]                 previous stage is multiplied
     float* sO = sQ + (size_t)Rcap * dk;            // [R][dv] un-normalised outputs
     float* sMax = sO + (size_t)Rcap * dv;          // [R] running maximum / sum / last rescale of this CTA
     float* sSum = sMax + Rcap;
@@ -165,25 +165,25 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
     const int nrg = nq * rep;                      // rows of one key / value head
     constexpr int RB = RBT;                        // rows of one key / value head a warp takes together
     const int nblk = (nrg + RB - 1) / RB;          // row blocks of one head
-    // a round = one tile of keys x one group of `gt` heads; this CTA's rounds in order, the next one's loads always in flight
+    // a stage = one tile of keys x one group of `gt` heads; this CTA's stages in order, the next one's loads always in flight
     const int ngrp = (G + p.gt - 1) / p.gt;
-    const int nround = rank < ntiles ? ((ntiles - rank + CL - 1) / CL) * ngrp : 0;
+    const int nstage = rank < ntiles ? ((ntiles - rank + CL - 1) / CL) * ngrp : 0;
     const size_t bufK = (size_t)p.gt * BA_KT * (dk + 4), bufV = (size_t)p.gt * BA_KT * (dv + 4);
-    auto load_round = [&](int rd) {
+    auto load_stage = [&](int rd) {
         const int ti = rank + (rd / ngrp) * CL, c0 = (rd % ngrp) * p.gt;
         const int j0 = ti * BA_KT;
         ba_load_tiles(p.cache, tbl, p.page, D, (size_t)c0 * dk, dk, (size_t)G * dk + (size_t)c0 * dv, dv, sK + (rd & 1) * bufK, tsk,
                       sV + (rd & 1) * bufV, tsv, min(p.gt, G - c0), min(BA_KT, pos1 + 1 - j0), j0, vec);
     };
-    if (nround > 0) load_round(0);
-    for (int rd = 0; rd < nround; ++rd) {
-        if (rd + 1 < nround) {
-            load_round(rd + 1);                    // into the buffer that round rd - 1 used: everyone left it at the barrier below
+    if (nstage > 0) load_stage(0);
+    for (int rd = 0; rd < nstage; ++rd) {
+        if (rd + 1 < nstage) {
+            load_stage(rd + 1);                    // into the buffer that stage rd - 1 used: everyone left it at the barrier below
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
-        __syncthreads();                           // round rd's tiles are visible (and, the first time, the rows are initialised)
+        __syncthreads();                           // stage rd's tiles are visible (and, the first time, the rows are initialised)
         {
             const int ti = rank + (rd / ngrp) * CL, c0 = (rd % ngrp) * p.gt;
             const int j0 = ti * BA_KT, nk = min(BA_KT, pos1 + 1 - j0), jl = j0 + lane;
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(BA_THREADS) bias_attn_kernel(const BiasAttnPar
                 __syncwarp();
             }
         }
-        __syncthreads();                           // everyone is done with round rd's buffers
+        __syncthreads();                           // everyone is done with stage rd's buffers
     }
     // the CTAs' partial results merged in rank order; every CTA finishes its share of the outputs
     cluster.sync();

@@ -345,6 +345,40 @@ def test_head_shapes(heads, kv_heads, dim, vdim):
         b.close()
 
 
+def random_model(seed):
+    """A configuration drawn at random: every size, count and constant of the family varies, layers differ from one another."""
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    blend_shape = (pick(1, 2, 3), pick(4, 8, 10, 24))          # (kv_heads, vdim) shared by the layers that blend values
+    layers = []
+    for _ in range(int(rng.integers(1, 5))):
+        blend = bool(rng.integers(2))
+        kv, vdim = blend_shape if blend else (pick(1, 2, 4), pick(4, 6, 16, 20, 36))
+        mlp = pick("dense", "moe", None)
+        experts, groups = pick((4, (2, 1)), (6, (3, 2)), (8, (8, 3)), (5, None), (9, (3, 3)), (2, (1, 1)))
+        per_kept = experts if not groups else experts // groups[0] * groups[1]
+        layers.append(L(heads=kv * pick(1, 2, 3, 4), kv_heads=kv, dim=pick(4, 8, 12, 18, 32, 40), vdim=vdim, scale=float(rng.uniform(0.1, 0.6)),
+                        bias_max=float(pick(21, 37.5, 64, 150, 1000)), v_mix=pick(True, None) if blend else pick(False, None), mlp=mlp,
+                        ff=pick(8, 24, 33), experts=experts, top=int(rng.integers(1, min(per_kept, 4) + 1)), groups=groups))
+    kw = dict(width=pick(24, 40, 56, 100), vocab=pick(31, 64, 150), streams=pick(None, 1, 2, 4, 6), embed_scale=pick(None, 0.25, 1.5),
+              rel_rows=pick(2, 5, 8, 13, 20, 32), eps=pick(1e-5, 1e-6, 1e-3))
+    return layers, kw
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(seed):
+    layers, kw = random_model(seed)
+    b = Bundle(layers, seed=seed, kv_page=int(np.random.default_rng(seed).choice([4, 8, 16, 64])), **kw)
+    try:
+        toks = b.tokens(150, seed)
+        want = b.oracle(toks)
+        assert err(b.feed(0, toks), want) <= TIGHT                                        # a prompt of two steps
+        out = [b.feed(1, toks[:57]), b.feed(1, toks[57:59])] + [b.feed(1, [t], capi.OPTION_LAST) for t in toks[59:110]] + [b.feed(1, toks[110:])]
+        assert err(np.concatenate(out), want) <= TIGHT                                    # portions, then decoding, then a portion
+    finally:
+        b.close()
+
+
 def test_serving_precision(stack_ref):
     toks, want = stack_ref
     b = Bundle(STACK, precision=0)
