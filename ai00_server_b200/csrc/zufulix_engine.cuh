@@ -139,7 +139,6 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
         l.attn_reg = dk % 4 == 0 && dv % 4 == 0 && dk <= 128 && dv <= 128;       // the register form of the attention kernel
         if (l.attn_reg) {
             while (qb > 1 && bias_attn_reg_smem(qb, H_, G_, dv, 4, 1) > 160 * 1024) qb /= 2;
-            REQUIRE(bias_attn_reg_smem(1, H_, G_, dv, 4, 8) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "too many attention heads for shared memory");
         } else {
             while (qb > 1 && bias_attn_smem(qb, H_, dk, dv, 1) > 112 * 1024) qb /= 2;   // two CTAs per SM where the heads allow it
             REQUIRE(bias_attn_smem(1, H_, dk, dv, 1) <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "attention heads too large for shared memory");
@@ -163,6 +162,7 @@ void b200rwkv_engine::zf_load(const StFile& st, KxSizes& z) {
     m.wa_ctas_prompt = m.wa_ctas_decode = 8;
     for (const KxLayer& l : m.layers) {
         const ZfAttnPlan pp = zf_attn_plan(l, qb, false), pd = zf_attn_plan(l, qb, true);
+        REQUIRE(pp.smem <= 200 * 1024 && pd.smem <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "too many attention heads for shared memory");
         int cl = 8, cl_ok = 0;
         for (; cl > 1; cl >>= 1) {
             bool ok = true;

@@ -330,7 +330,8 @@ def test_wider_layers(precision):
 # head sizes and head ratios around the attention kernel's two forms (registers: multiples of four up to 128; tiles in shared
 # memory: everything else), with 1 to 8 query heads per key / value head, in prompts of several chunks and in decoding
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(1, 1, 4, 4), (2, 2, 128, 128), (3, 1, 12, 100), (5, 1, 64, 8), (8, 1, 32, 32), (12, 4, 20, 24),
-                                                     (6, 3, 136, 16), (2, 1, 16, 132), (7, 7, 9, 6), (4, 2, 30, 34)])
+                                                     (6, 3, 136, 16), (2, 1, 16, 132), (7, 7, 9, 6), (4, 2, 30, 34), (32, 32, 8, 8), (40, 20, 4, 64),
+                                                     (16, 16, 64, 64)])
 def test_head_shapes(heads, kv_heads, dim, vdim):
     layers = [L(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, bias_max=50, mlp=None),
               L(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, bias_max=13, mlp="dense")]
