@@ -45,6 +45,7 @@ QUANT_NONE, QUANT_INT8, QUANT_NF4 = 0, 1, 2
 ARCH_KEMIRAX = 100          # Info.version of the config.json-described families
 ARCH_DEGAVIK = 101
 ARCH_ZUFULIX = 102
+ARCH_PASOPEL = 103
 
 
 class B200Error(RuntimeError):

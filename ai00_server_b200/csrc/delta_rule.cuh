@@ -25,11 +25,12 @@ namespace b200 {
 
 struct ShortConvParams {
     const float* x; int ldx;                      // [T, >= C] inputs (projection output rows)
-    float* y; int ldy;                            // [T, C] silu(conv)
+    float* y; int ldy;                            // [T, C] silu(conv), or conv
     const float* w;                               // [C][taps]
     float* tail;                                  // [S][taps - 1][C] of this layer; row taps - 2 is the most recent input
     int C, taps;
     MetaView meta;
+    int silu = 1;                                 // 0: the plain convolution
 };
 
 __global__ void __launch_bounds__(256) short_conv_kernel(const ShortConvParams p) {
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const ShortConvParams p
             const float xv = d <= back ? p.x[(size_t)(t - d) * p.ldx + c] : tl[(size_t)(p.taps - 1 + back - d) * p.C + c];
             acc = fmaf(p.w[(size_t)c * p.taps + j], xv, acc);
         }
-        p.y[(size_t)t * p.ldy + c] = acc / (1.f + expf(-acc));
+        p.y[(size_t)t * p.ldy + c] = p.silu ? acc / (1.f + expf(-acc)) : acc;
     }
 }
 

@@ -40,6 +40,7 @@
 #include "window_attn.cuh"
 #include "bias_attn.cuh"
 #include "hyper.cuh"
+#include "sink_attn.cuh"
 
 namespace b200 {
 
@@ -292,9 +293,11 @@ static b200rwkv_info derive_info(const StFile& st) {
     if (st.find("embed") && st.find("final.norm")) {      // families whose layer sizes are in a config.json
         const StTensor& e = *st.find("embed");
         // Kemirax norms are one gain; Degavik norms are weight vectors (and a layer may have no tensors of its own); Zufulix
-        // norms have a bias and the embedding table doubles as the output matrix
+        // norms have a bias and the embedding table doubles as the output matrix; Pasopel has vector norms without a bias and
+        // no separate output matrix either
         o.version = st.find("final.norm.b") ? B200RWKV_ARCH_ZUFULIX
-                                            : (st.find("final.norm")->numel() == 1 ? B200RWKV_ARCH_KEMIRAX : B200RWKV_ARCH_DEGAVIK);
+                    : st.find("final.norm")->numel() == 1 ? B200RWKV_ARCH_KEMIRAX
+                    : (st.find("head") ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_PASOPEL);
         o.num_vocab = (int)StFile::dim(e, 0, "embed", 2);
         o.num_emb = (int)StFile::dim(e, 1, "embed", 2);
         if (o.version != B200RWKV_ARCH_DEGAVIK) {
@@ -418,6 +421,7 @@ struct Snapshot { float* buf = nullptr; float* logits = nullptr; size_t bytes = 
 #include "kemirax.cuh"
 #include "degavik.cuh"
 #include "zufulix.cuh"
+#include "pasopel.cuh"
 
 using namespace b200;
 
@@ -530,6 +534,9 @@ struct b200rwkv_engine {
     void dg_enqueue_layer(cudaStream_t s, KxLayer& l, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
     void zf_load(const StFile& st, KxSizes& z);                   // Zufulix family (zufulix_engine.cuh)
     void zf_enqueue_layers(cudaStream_t s, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
+    void ps_load(const StFile& st, KxSizes& z);                   // Pasopel family (pasopel_engine.cuh)
+    void ps_enqueue_layers(cudaStream_t s, int rows, int nslot_grid, bool decode, int nsplit, Profiler* prof);
+    void ps_repool(int slot, int n);
     __nv_bfloat16* kx_up16(const std::vector<uint16_t>& v);
     float* kx_up32(const std::vector<float>& v);
     void kx_lin(cudaStream_t s, Profiler* prof, LinParams p, int rows, int groups, bool force_exact = false);
@@ -1838,6 +1845,7 @@ void b200rwkv_engine::state_xform(int slot, bool import, float* snap) {
 #include "kemirax_engine.cuh"
 #include "degavik_engine.cuh"
 #include "zufulix_engine.cuh"
+#include "pasopel_engine.cuh"
 
 // =========================================================================================
 // in-process tensor-parallel group

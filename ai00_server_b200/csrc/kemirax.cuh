@@ -106,8 +106,8 @@ private:
 // ------------------------------------------------------------------------------------------------------------------
 struct RotCfg { int dims = 0; double base = 10000.0; bool scaled = false; double factor = 1, original = 0, fast = 0, slow = 0; };
 
-enum KxMixer { KX_LATENT = 0, KX_GLA = 1, KX_RETENTION = 2, KX_DELTA = 3, KX_WINDOW = 4, KX_BIASED = 5 };
-enum KxFamily { KX_FAMILY_KEMIRAX = 0, KX_FAMILY_DEGAVIK = 1, KX_FAMILY_ZUFULIX = 2 };
+enum KxMixer { KX_LATENT = 0, KX_GLA = 1, KX_RETENTION = 2, KX_DELTA = 3, KX_WINDOW = 4, KX_BIASED = 5, KX_SINK = 6 };
+enum KxFamily { KX_FAMILY_KEMIRAX = 0, KX_FAMILY_DEGAVIK = 1, KX_FAMILY_ZUFULIX = 2, KX_FAMILY_PASOPEL = 3 };
 
 struct KxLayerCfg {
     int mixer = KX_LATENT;
@@ -124,6 +124,11 @@ struct KxLayerCfg {
     double bias_max = 0;                                         // distance from which every key shares the last bucket
     bool v_mix = false;                                          // values blended with the first such layer's
     int groups = 0, groups_keep = 0;                             // router: groups of neighbouring experts / groups kept (0: none)
+    // Pasopel (pasopel.cuh): attention whose values are its keys, behind short convolutions, over a window extended by block
+    // means, with a sink term; latent attention over a window with a sink term; a run of layers executed several times
+    int pool = 0;                                                // tokens per block mean behind the window (0: none)
+    int tensors_of = -1;                                         // index in the tensor names ("l<i>."); -1: the layer's own place
+    int opens_pass = -1;                                         // >= 0: this run opens pass number `opens_pass` of the looped layers
     int rot_dim = 0, kv_rank = 0, q_rank = 0, kv_from = -1;     // latent attention
     float scale = 1.f;
     RotCfg rot;
@@ -142,11 +147,14 @@ struct KxConfig {
     float eps = 1e-5f;
     int streams = 0;                                             // copies of the residual (0: the plain residual)
     float embed_scale = 1.f;                                     // factor on the embedding row
+    float logit_cap = 0.f;                                       // logits <- cap * tanh(logits / cap) (0: none)
+    bool has_loop = false;                                       // a run of layers is executed several times (`layers` lists every run)
     std::vector<KxLayerCfg> layers;
 };
 
 static KxConfig dg_parse_config(const JVal& root);
 static KxConfig zf_parse_config(const JVal& root);
+static KxConfig ps_parse_config(const JVal& root);
 
 // model registry of the families that come with a config.json: `architecture` names the design
 static KxConfig kx_parse_config(const char* json, size_t n) {
@@ -156,6 +164,7 @@ static KxConfig kx_parse_config(const char* json, size_t n) {
     const std::string arch = root.at("architecture").str;
     if (arch == "Degavik") return dg_parse_config(root);
     if (arch == "Zufulix") return zf_parse_config(root);
+    if (arch == "Pasopel") return ps_parse_config(root);
     REQUIRE(arch == "Kemirax", B200RWKV_ERR_UNSUPPORTED, "config: unknown architecture '" + arch + "'");
     KxConfig c;
     c.vocab = root.integer("vocab");
@@ -267,6 +276,10 @@ struct KxLayer {
     int gt_decode = 1;                                           // key / value heads per tile load in decode-shaped steps
     bool attn_reg = false;                                       // head sizes fit the attention kernel's register form
     float lam = 0.f;
+    // Pasopel: sink terms, output-gate offset in the projection row, block-mean rows, launch shape of the attention kernel
+    float *sink = nullptr, *o_b = nullptr, *pcache = nullptr;
+    int prow = 0;                                                // block-mean rows per page
+    int sa_hb = 1, sa_gt = 1, sa_gt_decode = 1, sa_nbuf = 2, sa_nbuf_decode = 2;
     // per-sequence memory of fixed size, in the order of the flat state record
     struct Block { float* base; size_t per_slot; };
     std::vector<Block> fixed;
@@ -288,6 +301,7 @@ struct SeqModel {
     float final_gain = 1.f;
     float* final_w = nullptr;                     // weight vector of the last norm (families that have one)
     float* final_b = nullptr;                     // its bias (layer-norm families)
+    float* pass_vec = nullptr;                    // [passes][W] vector a looped run of layers adds when a pass begins
     int streams = 1;                              // copies of the residual a token row of x holds
     float* vfirst = nullptr;                      // [T, G * dv] values of the first blending attention layer, this step's tokens
     int qb_prompt = 4;                            // tokens per attention chunk of a prompt step
@@ -309,6 +323,7 @@ struct SeqModel {
     float* lin_ws = nullptr; size_t lin_ws_floats = 0;
     float* dbg_layers = nullptr;                  // [L][maxT][W] residual after every layer (bring-up aid; nullptr: off)
     int max_split = 16;
+    int sa_ygroups = 1;                           // head groups (grid rows) of the smallest windowed-attention launch of the model
     SeqMeta sm{nullptr, 0};
     size_t flat_floats(int ctx_rows) const;
     int max_D = 0;

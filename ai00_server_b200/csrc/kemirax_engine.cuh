@@ -192,7 +192,9 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     m.W = m.cfg.width; m.V = m.cfg.vocab;
     const int W = m.W, nl = (int)m.cfg.layers.size();
     memset(&info, 0, sizeof(info));
-    info.version = m.cfg.family == KX_FAMILY_ZUFULIX ? B200RWKV_ARCH_ZUFULIX : (m.cfg.family == KX_FAMILY_DEGAVIK ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_KEMIRAX); info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
+    info.version = m.cfg.family == KX_FAMILY_PASOPEL ? B200RWKV_ARCH_PASOPEL
+                   : m.cfg.family == KX_FAMILY_ZUFULIX ? B200RWKV_ARCH_ZUFULIX
+                   : (m.cfg.family == KX_FAMILY_DEGAVIK ? B200RWKV_ARCH_DEGAVIK : B200RWKV_ARCH_KEMIRAX); info.num_layer = nl; info.num_emb = W; info.num_vocab = m.V;
     L = nl; C = W; V = m.V; Vl = V; Cl = C; H = Hl = 0; N = 0; F = Fl = 0;
     REQUIRE(world == 1, B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json run on one GPU in this version");
     REQUIRE(quant_layers == 0 && loras.empty(), B200RWKV_ERR_UNSUPPORTED, "models that come with a config.json take no LoRA / quantised layers");
@@ -224,7 +226,8 @@ void b200rwkv_engine::kx_build(const StFile& st, const char* cfg_json, size_t cf
     for (int i = m.npages - 1; i >= 0; --i) m.free_pages.push_back(i);
 
     KxSizes z;
-    if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_load(st, z);
+    if (m.cfg.family == KX_FAMILY_PASOPEL) ps_load(st, z);
+    else if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_load(st, z);
     else if (m.cfg.family == KX_FAMILY_DEGAVIK) dg_load(st, z);
     else kx_load(st, z);
     emb = nullptr;
@@ -323,8 +326,10 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         launch_k(embed_rows_kernel, dim3(rows), dim3(NORM_THREADS), 0, ep, KC_LN, s, prof);
     }
     const int nslot_grid = std::min(S, rows);
-    if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_enqueue_layers(s, rows, nslot_grid, decode, nsplit, prof);    // ends with the last norm
-    for (size_t li = 0; li < m.layers.size() && m.cfg.family != KX_FAMILY_ZUFULIX; ++li) {
+    const bool own_stack = m.cfg.family == KX_FAMILY_ZUFULIX || m.cfg.family == KX_FAMILY_PASOPEL;    // these end with the last norm
+    if (m.cfg.family == KX_FAMILY_ZUFULIX) zf_enqueue_layers(s, rows, nslot_grid, decode, nsplit, prof);
+    if (m.cfg.family == KX_FAMILY_PASOPEL) ps_enqueue_layers(s, rows, nslot_grid, decode, nsplit, prof);
+    for (size_t li = 0; li < m.layers.size() && !own_stack; ++li) {
         KxLayer& l = m.layers[li];
         const KxLayerCfg& c = l.c;
         if (m.cfg.family == KX_FAMILY_DEGAVIK) {
@@ -417,12 +422,13 @@ void b200rwkv_engine::kx_enqueue_step(cudaStream_t s, int rows, int rrows, bool 
         if (m.dbg_layers && !use_graph)
             CK(cudaMemcpyAsync(m.dbg_layers + li * (size_t)maxT * W, m.x, (size_t)maxT * W * 4, cudaMemcpyDeviceToDevice, s));
     }
-    if (m.cfg.family != KX_FAMILY_ZUFULIX) {
+    if (!own_stack) {
         FinalNormParams fn{m.x, m.hn, d_hidden, m.final_gain, m.cfg.eps, W, mv, m.final_w};
         launch_k(final_norm_kernel, dim3(rows), dim3(NORM_THREADS), 0, fn, KC_LN, s, prof);
     }
     if (rrows > 0) {
         LinParams ph = lin(m.hn, W, m.head, d_logits, V, V, W);
+        if (m.cfg.logit_cap > 0.f) { ph.epi = LE_TANH_CAP; ph.limit = m.cfg.logit_cap; }
         ph.cnt = cntR;
         kx_lin(s, prof, ph, rrows, 1);
     }
@@ -487,10 +493,12 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
         for (const KxLayer& l : m.layers) {
             if (l.c.mixer == KX_WINDOW) seen = std::max(seen, std::min(ctx_max, l.c.window + l.c.keep_first + QB));
             if (l.c.mixer == KX_BIASED) seen = std::max(seen, ctx_max);
+            if (m.cfg.family == KX_FAMILY_PASOPEL)         // the window, and one row per block of older tokens
+                seen = std::max(seen, std::min(ctx_max, l.c.window + QB) + (l.c.pool > 0 ? ctx_max / l.c.pool : 0));
         }
         const int tiles = cdiv(seen, WA_KT);
         ns = 1;
-        const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt);         // CTAs the GPU holds at once
+        const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt) / std::max(1, m.sa_ygroups);   // CTAs the GPU holds at once
         const int* cap = dec ? m.cl_cap_decode : m.cl_cap_prompt;
         auto lg2 = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
         while (ns < m.max_split && std::max(1, nch) * ns * 2 <= room && std::max(1, nch) <= cap[lg2(ns * 2)] && tiles / (ns * 2) >= 1)
@@ -587,6 +595,7 @@ void b200rwkv_engine::kx_xfer(int slot, float* rec, int ctx_rows, bool import, i
             o += (size_t)ctx_rows * l.cache_D;
         }
     }
+    if (import && m.cfg.family == KX_FAMILY_PASOPEL) ps_repool(slot, n);      // block means are derived from the cache rows
 }
 
 // host copy between two records of the same model whose cache blocks have different row counts

@@ -55,7 +55,16 @@ struct RopeParams {
     const float* freq;                             // [dims / 2]
     float mag;
     MetaView meta; SeqMeta sm;
+    const double* pair_freq = nullptr;             // set: neighbouring entries (2i, 2i + 1) turn together (angle reduced in double)
 };
+
+// the pair (2i, 2i + 1) of `s` turned by position * freq[i]; returns entry i of the result
+__device__ __forceinline__ float rot_pair_entry(const float* s, int i, int pos, const double* freq) {
+    float cs, sn;
+    rot_cos_sin(pos, freq[i >> 1], cs, sn);
+    const float u = s[i & ~1], v = s[i | 1];
+    return (i & 1) ? v * cs + u * sn : u * cs - v * sn;
+}
 
 __global__ void __launch_bounds__(128) rope_rows_kernel(const RopeParams p) {
     const int t = blockIdx.x;
@@ -67,6 +76,7 @@ __global__ void __launch_bounds__(128) rope_rows_kernel(const RopeParams p) {
         const float* s = p.src + (size_t)t * p.lds + (size_t)h * p.s_head + p.s_off;
         float* d = p.dst + (size_t)t * p.ldd + (size_t)h * p.d_head + p.d_off;
         if (i >= p.dims) { d[i] = s[i]; continue; }
+        if (p.pair_freq) { d[i] = rot_pair_entry(s, i, p.sm.tok_pos()[t], p.pair_freq); continue; }
         const int j = i < half ? i : i - half;
         const float a = pos * p.freq[j];
         const float cs = cosf(a) * p.mag, sn = sinf(a) * p.mag;
@@ -83,6 +93,7 @@ struct KvWriteParams {
     int rk, dr, dims;
     const float* freq; float mag, eps;
     MetaView meta; SeqMeta sm;
+    const double* pair_freq = nullptr;             // as in RopeParams
 };
 
 __global__ void __launch_bounds__(128) kv_write_kernel(const KvWriteParams p) {
@@ -111,6 +122,7 @@ __global__ void __launch_bounds__(128) kv_write_kernel(const KvWriteParams p) {
     for (int i = threadIdx.x; i < p.dr; i += blockDim.x) {
         const float* s = src + p.rk;
         if (i >= p.dims) { dst[p.rk + i] = s[i]; continue; }
+        if (p.pair_freq) { dst[p.rk + i] = rot_pair_entry(s, i, ipos, p.pair_freq); continue; }
         const int j = i < half ? i : i - half;
         const float a = pos * p.freq[j];
         const float cs = cosf(a) * p.mag, sn = sinf(a) * p.mag;

@@ -14,7 +14,8 @@
 //   lin_skinny_kernel        exact precision, a few rows: one warp per output pair, weight rows streamed as 16-byte loads, f32
 //                            FMA.
 //
-// Epilogues (fused): bias, sigmoid / silu / erf-gelu / squared relu, a per-row scale, accumulate-into-residual through a gate, and the gated units
+// Epilogues (fused): bias, sigmoid / silu / erf-gelu / squared relu / capped tanh, a sigmoid gate on the output, accumulate-into-residual
+// (plain or through a gate), and the gated units
 // (clamped, or plain silu(g) * u) on interleaved (gate, up) output pairs.
 #pragma once
 #include <cuda_bf16.h>
@@ -31,6 +32,9 @@ enum LinEpi {
     LE_GLU_SILU = 4,    // outputs (2i, 2i+1) = (g, u): Y[r, i] = g * sigmoid(g) * u
     LE_GELU_ERF = 5,    // Y = a * Phi(a), a = acc + bias, Phi the normal distribution function (erf form)
     LE_RELU_SQ = 6,     // Y = max(acc + bias, 0)^2
+    LE_ADD = 7,         // Y += acc + bias                 (residual accumulate; every element has one writer)
+    LE_MUL_SIGMOID = 8, // Y = (acc + bias) * sigmoid(gate[r, n])   (group g reads gate + g * gate_gstride)
+    LE_TANH_CAP = 9,    // Y = limit * tanh((acc + bias) / limit)
 };
 
 struct LinParams {
@@ -42,8 +46,9 @@ struct LinParams {
     const int* off;                                    // first compact row of group g (nullptr: 0)
     const int* xlist;                                  // X row of compact row i (nullptr: i)
     const float* bias;                                 // [N] (nullptr: none); group g adds g * N
-    const float* gate; int ldg;                        // LE_GATED_ADD
-    float limit;                                       // LE_GLU_CLAMP
+    const float* gate; int ldg;                        // LE_GATED_ADD, LE_MUL_SIGMOID
+    long long gate_gstride;                            // LE_MUL_SIGMOID: gate + g * gate_gstride
+    float limit;                                       // LE_GLU_CLAMP, LE_TANH_CAP
     int epi;
     int max_rows;                                      // upper bound of any group's rows (grid sizing)
     // split-k (tensor-core tile kernel, one group): blockIdx.x = split * n_tiles + n_tile, split s multiplies its own range of
@@ -84,6 +89,9 @@ __device__ __forceinline__ void lin_store(const LinParams& p, int g, int yrow, i
         else if (p.epi == LE_GELU_ERF) *y = 0.5f * a * (1.f + erff(a * 0.70710678118654752f));
         else if (p.epi == LE_RELU_SQ) { const float r = fmaxf(a, 0.f); *y = r * r; }
         else if (p.epi == LE_GATED_ADD) *y += p.gate[(size_t)yrow * p.ldg + nn] * a;
+        else if (p.epi == LE_ADD) *y += a;
+        else if (p.epi == LE_MUL_SIGMOID) *y = a * lin_sigmoid(p.gate[g * p.gate_gstride + (size_t)yrow * p.ldg + nn]);
+        else if (p.epi == LE_TANH_CAP) *y = p.limit * tanhf(a / p.limit);
         else *y = a;
     }
 }

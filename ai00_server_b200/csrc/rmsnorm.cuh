@@ -7,6 +7,9 @@
 //   final_norm_kernel      rows that want logits: x[out_tok[r]] / rms * g  -> compact [R, W] head operand (+ all hidden rows);
 //                          g = one scalar gain or a weight vector
 //   norm_add_kernel        x += y / rms(y) * w: the norm sits on a sublayer's output (optionally combining routed expert rows first)
+//   pre_norm_kernel        the boundary in front of a pre-norm sublayer in one pass: the routed experts that just finished are
+//                          combined into the residual, a looped run of layers that begins adds the embedding row and its pass
+//                          vector, and the normed row (or, at the end of the stack, the compact rows that want logits) is written
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -193,6 +196,73 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_add_kernel(const NormAddPar
         const float f = p.rows ? norm_add_row[c] : p.y[(size_t)t * W + c];
         p.x[(size_t)t * W + c] += f * r * p.weight[c];
     }
+}
+
+// The boundary in front of a pre-norm sublayer.  In this order, each part optional:
+//   x[t] += sum_k wgt[t, k] rows[row_of[t, k]] + shared[t]     the routed feed-forward that just finished (its combine step)
+//   snap[t] = x[t]                                             the residual as the finished layer leaves it (bring-up aid)
+//   x[t] += table[token[t]] + vec                              a pass of a looped run of layers begins
+//   h[t] = x[t] / rms(x[t]) * weight                           the sublayer's input; `weight` holds the whole factor (a model
+//                                                              that stores offsets from one uploads 1 + w)
+// With `compact` only the rows that want logits are normed and land in h[row]; `hidden` gets a copy of every residual row.
+// All f32.  Dynamic shared memory: W floats.
+struct PreNormParams {
+    float* x;                 // [T, W] residual, updated in place
+    const float* rows;        // [T * top, W] expert outputs in compact rows (nullptr: nothing pending)
+    const int* row_of; const float* wgt; int top;
+    const float* shared;      // [T, W] (nullptr: none)
+    float* snap;              // [T, W] (nullptr: none)
+    const __nv_bfloat16* table;   // [vocab, W] (nullptr: none)
+    const float* vec;         // [W] (nullptr: none)
+    const float* weight;      // [W] (nullptr: no norm, x is only updated)
+    float eps;
+    float* h;                 // [T, W], or [R, W] with compact
+    int compact;
+    float* hidden;            // [T, W] (nullptr: none)
+    int W;
+    MetaView meta;
+};
+
+__global__ void __launch_bounds__(NORM_THREADS) pre_norm_kernel(const PreNormParams p) {
+    __shared__ float red[32];
+    extern __shared__ __align__(16) float pre_norm_row[];      // [W]
+    const int t = blockIdx.x;
+    if (t >= p.meta.T()) return;
+    const int W = p.W;
+    float* xr = p.x + (size_t)t * W;
+    int rw[NORM_ADD_MAX_TOP]; float wg[NORM_ADD_MAX_TOP];
+    if (p.rows) {
+#pragma unroll
+        for (int k = 0; k < NORM_ADD_MAX_TOP; ++k)
+            if (k < p.top) { rw[k] = p.row_of[(size_t)t * p.top + k]; wg[k] = p.wgt[(size_t)t * p.top + k]; }
+    }
+    const __nv_bfloat16* er = p.table ? p.table + (size_t)p.meta.tok()[t] * W : nullptr;
+    const bool writes = p.rows || er || p.vec;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float v = xr[c];
+        if (p.rows) {
+            float f = 0.f;
+#pragma unroll
+            for (int k = 0; k < NORM_ADD_MAX_TOP; ++k)
+                if (k < p.top) f = fmaf(wg[k], p.rows[(size_t)rw[k] * W + c], f);
+            if (p.shared) f += p.shared[(size_t)t * W + c];
+            v += f;
+        }
+        if (p.snap) p.snap[(size_t)t * W + c] = v;
+        if (er) v += __bfloat162float(er[c]);
+        if (p.vec) v += p.vec[c];
+        if (writes) xr[c] = v;
+        if (p.hidden) p.hidden[(size_t)t * W + c] = v;
+        pre_norm_row[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!p.weight) return;
+    const int row = p.compact ? p.meta.tok_outrow()[t] : t;
+    if (row < 0) return;
+    ss = rms_block_sum(ss, red);
+    const float r = 1.f / sqrtf(ss / (float)W + p.eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) p.h[(size_t)row * W + c] = pre_norm_row[c] * r * p.weight[c];
 }
 
 }  // namespace b200

@@ -1,0 +1,309 @@
+// Softmax attention over a paged cache with a sliding window, a learned "sink" term per head in the softmax denominator, and
+// (optionally) block means of the keys / values that have left the window.  No positions enter the scores here: a layer that
+// rotates its queries and keys does so before it calls this.
+//
+// H query heads, G key / value heads (query head h reads head h / (H / G)).  A cache row of D floats holds, for every key /
+// value head c, a key of dk floats at `koff + c dk` and a value of dv floats at `voff + c dv` (the two may be the same floats:
+// a latent row that is scored against and summed, G = 1).  For query position i:
+//     tokens   j with  i - win < j <= i
+//     blocks   b with  (b + 1) pool <= i - win + 1      (pool > 0): the mean of the cache rows b pool .. b pool + pool - 1,
+//              kept in a second pool of rows with the same layout (pool_write_kernel) so that a block costs one row to read
+//     s_h(i, u) = (q_h(i) . k(u)) * scale           over the visible tokens and blocks u together
+//     o_h(i) = sum_u exp(s_h(i, u)) v(u) / (exp(sink_h) + sum_u exp(s_h(i, u)))        * sigmoid(gate_h(i))  (gate optional)
+//
+//   pool_write_kernel     every token of the step that closes a block writes the block's mean row (sums in position order, f32)
+//   pool_rebuild_kernel   the same for all closed blocks of one sequence (after a state import)
+//   sink_attn_kernel      a cluster of 1..8 CTAs per (chunk of consecutive tokens of one sequence, group of HB query heads);
+//                         the visible block rows and then the window's token rows form 32-key tiles that are dealt out among
+//                         the cluster's CTAs; every CTA walks its tiles once with a running maximum / sum per (token, head) row
+//                         and the partial results are merged through distributed shared memory in rank order, where the sink
+//                         and the gate come in.  A warp owns 1, 2 or 4 rows of one key / value head (template).  Tiles arrive
+//                         by cp.async into one or two buffers.  Scores, weights and sums in f32.  Any head size.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include "common.cuh"
+#include "latent_attn.cuh"
+#include "linear.cuh"
+
+namespace b200 {
+
+// row of pooled block b of a sequence: the block lives in the page of its first position
+__device__ __forceinline__ size_t sa_pool_row(const int* tbl, int page, int pool, int prow, int b) {
+    const int p0 = b * pool, pg = p0 / page;
+    return (size_t)tbl[pg] * prow + (size_t)((p0 - pg * page) / pool);
+}
+__device__ __forceinline__ size_t sa_token_row(const int* tbl, int page, int j) {
+    const int pg = j / page;
+    return (size_t)tbl[pg] * page + (size_t)(j - pg * page);
+}
+
+struct PoolWriteParams {
+    const float* cache; float* pcache;             // [pages][page][D], [pages][prow][D]
+    const int* table; int stride, page;
+    int D, pool, prow;
+    int slot, nblocks;                             // pool_rebuild_kernel: the sequence and its closed blocks
+    MetaView meta; SeqMeta sm;
+};
+
+__device__ __forceinline__ void sa_pool_block(const PoolWriteParams& p, const int* tbl, int b) {
+    float* dst = p.pcache + sa_pool_row(tbl, p.page, p.pool, p.prow, b) * p.D;
+    const float inv = 1.f / (float)p.pool;
+    for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
+        float s = 0.f;
+        for (int u = 0; u < p.pool; ++u) s += p.cache[sa_token_row(tbl, p.page, b * p.pool + u) * p.D + d];
+        dst[d] = s * inv;
+    }
+}
+
+__global__ void __launch_bounds__(128) pool_write_kernel(const PoolWriteParams p) {
+    const int t = blockIdx.x;
+    if (t >= p.meta.T()) return;
+    const int ipos = p.sm.tok_pos()[t];
+    if ((ipos + 1) % p.pool != 0) return;
+    sa_pool_block(p, p.table + (size_t)p.meta.tok_slot()[t] * p.stride, ipos / p.pool);
+}
+
+__global__ void __launch_bounds__(128) pool_rebuild_kernel(const PoolWriteParams p) {
+    if ((int)blockIdx.x < p.nblocks) sa_pool_block(p, p.table + (size_t)p.slot * p.stride, blockIdx.x);
+}
+
+struct SinkAttnParams {
+    const float* q; int ldq;                       // query of (t, h): q + t ldq + h dk
+    const float* cache; const float* pcache;       // token rows; block-mean rows (nullptr / pool = 0: none)
+    const int* table; int stride, page;
+    int D, koff, voff;
+    float* out; int ldo;                           // [T, H dv]
+    const float* gate; int ldg;                    // out *= sigmoid(gate[t ldg + h dv + d])   (nullptr: no gate)
+    const float* sink;                             // [H] (nullptr: no sink term)
+    float scale;
+    int H, G, dk, dv, HB;                          // HB query heads per CTA: a multiple of H / G, or a divisor of it
+    int win, pool, prow;
+    int qb;                                        // tokens per chunk the shared memory was sized for
+    int gt;                                        // key / value heads per tile load
+    int cl;                                        // CTAs per chunk (cluster size)
+    int nbuf;                                      // tile buffers (2: the next tile loads while this one is multiplied)
+    int valias;                                    // the value is the first dv floats of the key (one tile serves both)
+    MetaView meta; SeqMeta sm;
+};
+
+constexpr int SA_KT = 32;                          // keys per tile (one per lane in the score phase)
+constexpr int SA_THREADS = 512;                    // most threads per CTA; the host launches 256 where fewer warps find work
+constexpr int SA_RB = 4;                           // most rows of one key / value head a warp works on together
+
+__host__ __device__ inline size_t sink_attn_smem(int qb, int HB, int dk, int dv, int gt, int nbuf, bool valias) {
+    const size_t R = (size_t)qb * HB;
+    return (R * dk + R * dv + R * SA_KT + (size_t)nbuf * gt * SA_KT * ((dk + 4) + (valias ? 0 : dv + 4)) + 3 * R + 8) * sizeof(float);
+}
+
+template <int RBT>
+__global__ void __launch_bounds__(SA_THREADS) sink_attn_kernel(const SinkAttnParams p) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int CL = p.cl, rank = blockIdx.x % CL, ch = blockIdx.x / CL;
+    if (ch >= p.sm.n_chunks()) return;             // the same for every CTA of a cluster
+    const int t0 = p.sm.chunk_start()[ch], nq = p.sm.chunk_count()[ch];
+    const int slot = p.meta.tok_slot()[t0];
+    const int pos0 = p.sm.tok_pos()[t0], pos1 = pos0 + nq - 1;
+    const int H = p.H, dk = p.dk, dv = p.dv, rep = H / p.G;
+    const int h0 = blockIdx.y * p.HB, nh = min(p.HB, H - h0);       // query heads of this CTA
+    const int c_first = h0 / rep, nhc = min(rep, nh), ncv = nh / nhc;   // first key head, query heads per key head, key heads
+    const int R = nq * nh, D = p.D;
+    const bool valias = p.valias != 0;
+    // sizes that are multiples of four: tile rows start on 16 bytes (stride d + 4: a quarter warp's 16-byte reads of eight
+    // different rows fall into different banks) and arrive by cp.async; otherwise stride d + 1 and scalar loads
+    const bool vec = (dk % 4 == 0) && (dv % 4 == 0) && (D % 4 == 0) && (p.koff % 4 == 0) && (p.voff % 4 == 0);
+    const int tsk = dk + (vec ? 4 : 1), tsv = valias ? tsk : dv + (vec ? 4 : 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    extern __shared__ __align__(16) float sa_smem[];
+    const int Rcap = p.qb * p.HB;
+    const size_t bufK = (size_t)p.gt * SA_KT * (dk + 4), bufV = valias ? 0 : (size_t)p.gt * SA_KT * (dv + 4);
+    float* sP = sa_smem;                           // [R][KT] weights of the tile
+    float* sK = sP + (size_t)Rcap * SA_KT;         // [nbuf][gt][KT][tsk]
+    float* sV = sK + (size_t)p.nbuf * bufK;        // [nbuf][gt][KT][tsv]
+    float* sQ = sV + (size_t)p.nbuf * bufV;        // [R][dk]
+    float* sO = sQ + (size_t)Rcap * dk;            // [R][dv] un-normalised outputs
+    float* sMax = sO + (size_t)Rcap * dv;          // [R] running maximum / sum / last rescale of this CTA
+    float* sSum = sMax + Rcap;
+    float* sScl = sSum + Rcap;
+    for (int e = threadIdx.x; e < R * dk; e += (int)blockDim.x) {
+        const int r = e / dk, i = e % dk;
+        sQ[e] = p.q[(size_t)(t0 + r / nh) * p.ldq + (size_t)(h0 + r % nh) * dk + i];
+    }
+    for (int e = threadIdx.x; e < R * dv; e += (int)blockDim.x) sO[e] = 0.f;
+    for (int e = threadIdx.x; e < R; e += (int)blockDim.x) { sMax[e] = -CUDART_INF_F; sSum[e] = 0.f; sScl[e] = 1.f; }
+    // what the chunk can see: the blocks its last token sees, then the tokens from the first token's window edge on
+    const int npb = p.pool > 0 ? max(0, pos1 - p.win + 1) / p.pool : 0;
+    const int jlo = max(0, pos0 - p.win + 1), ntk = pos1 - jlo + 1;
+    const int npt = (npb + SA_KT - 1) / SA_KT, ntiles = npt + (ntk + SA_KT - 1) / SA_KT;
+    const int* tbl = p.table + (size_t)slot * p.stride;
+    const int nrg = nq * nhc;                      // rows of one key / value head
+    constexpr int RB = RBT;
+    const int nblk = (nrg + RB - 1) / RB;          // row blocks of one head
+    // a stage = one tile of keys x one group of `gt` heads; this CTA's stages in order
+    const int ngrp = (ncv + p.gt - 1) / p.gt;
+    const int nstage = rank < ntiles ? ((ntiles - rank + CL - 1) / CL) * ngrp : 0;
+    auto load_stage = [&](int rd) {
+        const int ti = rank + (rd / ngrp) * CL, g0 = (rd % ngrp) * p.gt, gn = min(p.gt, ncv - g0);
+        const bool pooled = ti < npt;
+        const int i0 = pooled ? ti * SA_KT : jlo + (ti - npt) * SA_KT;          // first block / position of the tile
+        const int nk = pooled ? min(SA_KT, npb - i0) : min(SA_KT, pos1 + 1 - i0);
+        float* tk = sK + (size_t)(rd % p.nbuf) * bufK;
+        float* tv = sV + (size_t)(rd % p.nbuf) * bufV;
+        const size_t offk = (size_t)p.koff + (size_t)(c_first + g0) * dk, offv = (size_t)p.voff + (size_t)(c_first + g0) * dv;
+        for (int kt = warp; kt < SA_KT; kt += nw) {
+            if (kt >= nk) {                        // rows past the tile's keys: their weights are zero and 0 * junk must stay 0
+                for (int c = 0; c < gn; ++c) {
+                    if (valias) for (int i = lane; i < dv; i += 32) tk[((size_t)c * SA_KT + kt) * tsk + i] = 0.f;
+                    else for (int i = lane; i < dv; i += 32) tv[((size_t)c * SA_KT + kt) * tsv + i] = 0.f;
+                }
+                continue;
+            }
+            const float* src = pooled ? p.pcache + sa_pool_row(tbl, p.page, p.pool, p.prow, i0 + kt) * D
+                                      : p.cache + sa_token_row(tbl, p.page, i0 + kt) * D;
+            for (int c = 0; c < gn; ++c) {
+                float* dk_ = tk + ((size_t)c * SA_KT + kt) * tsk;
+                float* dv_ = tv + ((size_t)c * SA_KT + kt) * tsv;
+                if (vec) {
+                    for (int v4 = lane; v4 < (dk >> 2); v4 += 32) cp_async16(dk_ + v4 * 4, src + offk + (size_t)c * dk + v4 * 4);
+                    if (!valias) for (int v4 = lane; v4 < (dv >> 2); v4 += 32) cp_async16(dv_ + v4 * 4, src + offv + (size_t)c * dv + v4 * 4);
+                } else {
+                    for (int i = lane; i < dk; i += 32) dk_[i] = src[offk + (size_t)c * dk + i];
+                    if (!valias) for (int i = lane; i < dv; i += 32) dv_[i] = src[offv + (size_t)c * dv + i];
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    if (nstage > 0 && p.nbuf > 1) load_stage(0);
+    for (int rd = 0; rd < nstage; ++rd) {
+        if (p.nbuf > 1) {
+            if (rd + 1 < nstage) {
+                load_stage(rd + 1);                // into the buffer that stage rd - 1 used: everyone left it at the barrier below
+                asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            }
+        } else {
+            load_stage(rd);
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();                           // stage rd's tiles are visible (and, the first time, the rows are initialised)
+        {
+            const int ti = rank + (rd / ngrp) * CL, g0 = (rd % ngrp) * p.gt, gn = min(p.gt, ncv - g0);
+            const bool pooled = ti < npt;
+            const int i0 = pooled ? ti * SA_KT : jlo + (ti - npt) * SA_KT;
+            const int nk = pooled ? min(SA_KT, npb - i0) : min(SA_KT, pos1 + 1 - i0);
+            const int il = i0 + lane;              // this lane's block or position
+            const float* cK = sK + (size_t)(rd % p.nbuf) * bufK;
+            const float* cV = valias ? cK : sV + (size_t)(rd % p.nbuf) * bufV;
+            for (int it = warp; it < gn * nblk; it += nw) {
+                const int cl_ = it / nblk, lc = g0 + cl_, rr0 = (it % nblk) * RB, nr = min(RB, nrg - rr0);
+                int rows[RBT];
+                const float* qv[RBT];
+#pragma unroll
+                for (int b = 0; b < RBT; ++b) {
+                    const int rr = rr0 + min(b, nr - 1);
+                    rows[b] = (rr / nhc) * nh + lc * nhc + rr % nhc;
+                    qv[b] = sQ + (size_t)rows[b] * dk;
+                }
+                // ---- scores of the warp's rows against key `lane` ----
+                float sc[RBT];
+#pragma unroll
+                for (int b = 0; b < RBT; ++b) sc[b] = 0.f;
+                if (lane < nk) {
+                    const float* kv = cK + ((size_t)cl_ * SA_KT + lane) * tsk;
+                    if (vec) {
+                        const float4* k4 = reinterpret_cast<const float4*>(kv);
+#pragma unroll 4
+                        for (int i = 0; i < dk / 4; ++i) {
+                            const float4 kx = k4[i];
+#pragma unroll
+                            for (int b = 0; b < RBT; ++b) {
+                                const float4 qx = reinterpret_cast<const float4*>(qv[b])[i];
+                                sc[b] = fmaf(qx.x, kx.x, sc[b]); sc[b] = fmaf(qx.y, kx.y, sc[b]);
+                                sc[b] = fmaf(qx.z, kx.z, sc[b]); sc[b] = fmaf(qx.w, kx.w, sc[b]);
+                            }
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int i = 0; i < dk; ++i) {
+                            const float kx = kv[i];
+#pragma unroll
+                            for (int b = 0; b < RBT; ++b) sc[b] = fmaf(qv[b][i], kx, sc[b]);
+                        }
+                    }
+                }
+                // ---- running maximum / sum of every row, the tile's weights ----
+#pragma unroll
+                for (int b = 0; b < RBT; ++b) {
+                    if (b >= nr) break;
+                    const int r = rows[b], pq = pos0 + r / nh;
+                    const bool vis = lane < nk && (pooled ? il < max(0, pq - p.win + 1) / p.pool : (il <= pq && il > pq - p.win));
+                    const float s = vis ? sc[b] * p.scale : -CUDART_INF_F;
+                    float mx = s;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                    const float mo = sMax[r], mn = fmaxf(mo, mx);
+                    float e = vis ? expf(s - mn) : 0.f;        // mn is finite wherever a key is visible
+                    sP[r * SA_KT + lane] = e;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) e += __shfl_xor_sync(0xffffffffu, e, o);
+                    __syncwarp();                              // everyone has read the old maximum
+                    if (lane == 0) {
+                        const float scl = mo > -CUDART_INF_F ? expf(mo - mn) : (mn > -CUDART_INF_F ? 0.f : 1.f);
+                        sScl[r] = scl;
+                        sSum[r] = sSum[r] * scl + e;
+                        sMax[r] = mn;
+                    }
+                }
+                __syncwarp();
+                // ---- weights x values ----
+                const float* vt = cV + (size_t)cl_ * SA_KT * tsv;
+                for (int d = lane; d < dv; d += 32) {
+                    float acc[RBT];
+#pragma unroll
+                    for (int b = 0; b < RBT; ++b) acc[b] = sO[(size_t)rows[b] * dv + d] * sScl[rows[b]];
+#pragma unroll 2
+                    for (int kt = 0; kt < SA_KT; kt += 4) {
+                        const float v0 = vt[(kt + 0) * tsv + d], v1 = vt[(kt + 1) * tsv + d], v2 = vt[(kt + 2) * tsv + d], v3 = vt[(kt + 3) * tsv + d];
+#pragma unroll
+                        for (int b = 0; b < RBT; ++b) {
+                            const float4 w4 = *reinterpret_cast<const float4*>(sP + rows[b] * SA_KT + kt);
+                            acc[b] = fmaf(w4.x, v0, acc[b]); acc[b] = fmaf(w4.y, v1, acc[b]);
+                            acc[b] = fmaf(w4.z, v2, acc[b]); acc[b] = fmaf(w4.w, v3, acc[b]);
+                        }
+                    }
+#pragma unroll
+                    for (int b = 0; b < RBT; ++b)
+                        if (b < nr) sO[(size_t)rows[b] * dv + d] = acc[b];
+                }
+                __syncwarp();
+            }
+        }
+        __syncthreads();                           // everyone is done with stage rd's buffers
+    }
+    // the CTAs' partial results merged in rank order, the sink joins the denominator; every CTA finishes its share of the outputs
+    cluster.sync();
+    for (int e = rank * (int)blockDim.x + threadIdx.x; e < R * dv; e += CL * (int)blockDim.x) {
+        const int r = e / dv, d = e % dv, t = t0 + r / nh, h = h0 + r % nh;
+        float m = p.sink ? p.sink[h] : -CUDART_INF_F;
+        for (int rk = 0; rk < CL; ++rk) m = fmaxf(m, cluster.map_shared_rank(sMax, rk)[r]);
+        float num = 0.f, den = p.sink ? expf(p.sink[h] - m) : 0.f;
+        for (int rk = 0; rk < CL; ++rk) {
+            const float mr = cluster.map_shared_rank(sMax, rk)[r];
+            if (mr > -CUDART_INF_F) {
+                const float f = expf(mr - m);
+                num = fmaf(cluster.map_shared_rank(sO, rk)[e], f, num);
+                den = fmaf(cluster.map_shared_rank(sSum, rk)[r], f, den);
+            }
+        }
+        float o = num / den;
+        if (p.gate) o *= lin_sigmoid(p.gate[(size_t)t * p.ldg + (size_t)h * dv + d]);
+        p.out[(size_t)t * p.ldo + (size_t)h * dv + d] = o;
+    }
+    cluster.sync();                                // nobody leaves while its shared memory is still being read
+}
+
+}  // namespace b200

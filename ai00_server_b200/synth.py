@@ -565,3 +565,102 @@ def make_zufulix(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e
     bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
     rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
     return json.dumps(cfg).encode(), pack_st_bf16(t), rounded
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# Pasopel family (config.json + bf16 safetensors): random weights for tests and bench.py
+# ----------------------------------------------------------------------------------------------------------------------
+def pasopel_layer(kind: str, *, heads=4, kv_heads=None, dim=16, vdim=None, conv=3, window=8, pool=4, rot_dim=8, rot_dims=None, kv_rank=24,
+                  q_rank=20, base=10000.0, scale=None, mlp="dense", ff=48, experts=8, top=2, shared_ff=24) -> dict:
+    """One entry of config['layers'].  kind: 'attention' | 'latent_attention'; mlp: 'dense' | 'moe' | None; pool 0: no block means."""
+    if kind == "attention":
+        mixer = {"heads": heads, "kv_heads": int(kv_heads or heads), "dim": dim, "vdim": dim, "conv": int(conv),
+                 "scale": float(scale if scale is not None else dim ** -0.5), "mask": {"size": int(window)}}
+        if pool:
+            mixer["mask"]["pool"] = int(pool)
+    elif kind == "latent_attention":
+        mixer = {"heads": heads, "dim": dim, "rot_dim": int(rot_dim), "vdim": int(vdim or dim), "kv_rank": int(kv_rank), "q_rank": int(q_rank),
+                 "rot": {"base": float(base), "dims": int(rot_dim if rot_dims is None else rot_dims)},
+                 "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5), "mask": {"size": int(window)}}
+    else:
+        raise ValueError(kind)
+    layer = {"type": kind, "mixer": mixer, "mlp": None}
+    if mlp == "dense":
+        layer["mlp"] = {"kind": "dense", "ff": int(ff)}
+    elif mlp == "moe":
+        layer["mlp"] = {"kind": "moe", "router": {"experts": int(experts), "top": int(top)}, "expert": {"ff": int(ff)}}
+        if shared_ff:
+            layer["mlp"]["shared"] = {"ff": int(shared_ff)}
+    return layer
+
+
+def make_pasopel(layers: list, width: int = 64, vocab: int = 96, eps: float = 1e-5, seed: int = 0, loop: tuple | None = (0, 1, 2),
+                 softcap: float | None = 12.0, arrays: bool = True, sink_gain: float = 1.0):
+    """(config.json bytes, safetensors image, dict of float64 arrays holding the bf16-rounded values, or None when `arrays` is
+    off) for a random model of the family.  loop: (start, stop, times) or None."""
+    rng = np.random.default_rng(seed)
+    W = width
+    t = {}
+
+    def mat(n, k, g=1.0):
+        return (rng.standard_normal((n, k)) * (g / np.sqrt(k))).astype(np.float32)
+
+    def norm(name, n=W):
+        t[name] = (0.3 * rng.standard_normal(n)).astype(np.float32)
+
+    def unit(p, ff):
+        t[p + "gate"] = mat(ff, W, 2.0)
+        t[p + "up"] = mat(ff, W, 2.0)
+        t[p + "down"] = mat(W, ff)
+
+    t["embed"] = rng.standard_normal((vocab, W)).astype(np.float32)
+    if loop is not None:
+        t["loop.step"] = (0.5 * rng.standard_normal((loop[2], W))).astype(np.float32)
+    for i, l in enumerate(layers):
+        p, m = "l%d." % i, l["mixer"]
+        H, dk, dv = m["heads"], m["dim"], m["vdim"]
+        norm(p + "norm1")
+        if l["type"] == "attention":
+            G = m.get("kv_heads", H)
+            for n, rows in (("q", H * dk), ("k", G * dk)):
+                t[p + "mix." + n] = mat(rows, W, 2.0)
+                t[p + "mix." + n + ".b"] = (0.3 * rng.standard_normal(rows)).astype(np.float32)
+                t[p + "mix." + n + ".conv"] = (rng.standard_normal((rows, m["conv"])) * 0.6).astype(np.float32)
+            t[p + "mix.o.b"] = (0.1 * rng.standard_normal(W)).astype(np.float32)
+        else:
+            dr, rk, rq = m["rot_dim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"] = mat(rq, W)
+            t[p + "mix.dq.norm"] = rng.uniform(0.5, 1.5, rq).astype(np.float32)
+            t[p + "mix.uq"] = mat(H * (dk + dr), rq, 2.0)
+            t[p + "mix.dkv"] = mat(rk + dr, W, 2.0)
+            t[p + "mix.dkv.norm"] = rng.uniform(0.5, 1.5, rk).astype(np.float32)
+            t[p + "mix.uk"] = mat(H * dk, rk, 2.0)
+            t[p + "mix.uv"] = mat(H * dv, rk)
+        t[p + "mix.sink"] = (sink_gain * rng.standard_normal(H)).astype(np.float32)
+        t[p + "mix.g"] = mat(H * dv, W, 2.0)
+        t[p + "mix.o"] = mat(W, H * dv)
+        f = l.get("mlp")
+        if f:
+            norm(p + "norm2")
+            if f["kind"] == "dense":
+                t[p + "mlp.up"] = mat(f["ff"], W, 2.0)
+                t[p + "mlp.down"] = mat(W, f["ff"])
+            else:
+                E = f["router"]["experts"]
+                t[p + "mlp.router"] = mat(E, W, 3.0)
+                t[p + "mlp.router.b"] = rng.uniform(-0.5, 0.5, E).astype(np.float32)
+                for e in range(E):
+                    unit(p + "mlp.e%d." % e, f["expert"]["ff"])
+                if f.get("shared"):
+                    unit(p + "mlp.shared.", f["shared"]["ff"])
+    norm("final.norm")
+    cfg = {"architecture": "Pasopel", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": W}
+    if loop is not None:
+        cfg["loop"] = {"start": int(loop[0]), "stop": int(loop[1]), "times": int(loop[2])}
+    if softcap is not None:
+        cfg["logit_softcap"] = float(softcap)
+    if not arrays:
+        return json.dumps(cfg).encode(), pack_st_bf16(t), None
+    bits = {k: to_bf16_bits(np.asarray(v, np.float32).reshape(np.shape(v))) for k, v in t.items()}
+    rounded = {k: (b.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(t[k])).astype(np.float64) for k, b in bits.items()}
+    return json.dumps(cfg).encode(), pack_st_bf16(t), rounded

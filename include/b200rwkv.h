@@ -103,8 +103,9 @@ typedef struct {
     /* Model families that are described by a config.json beside the weights (architecture "Kemirax": parallel blocks of latent
      * attention / gated linear attention + routed experts; architecture "Degavik": blocks normed on the sublayer outputs with
      * retention / gated delta rule / windowed attention mixers and dense or routed feed-forwards; architecture "Zufulix": pre-norm
-     * blocks around several copies of the residual with distance-biased attention and dense or group-routed feed-forwards; bf16
-     * weights): the JSON text, borrowed during the call.  NULL: the
+     * blocks around several copies of the residual with distance-biased attention and dense or group-routed feed-forwards;
+     * architecture "Pasopel": pre-norm blocks, a run of layers executed several times, windowed attention with block means and
+     * a sink term, windowed latent attention, dense or routed feed-forwards; bf16 weights): the JSON text, borrowed during the call.  NULL: the
      * family is recognised from the tensor names (RWKV v5 / v6 / v7).  Such models keep an attention cache in pages of
      * `kv_page` tokens (0 = 64) drawn from a pool sized for `kv_tokens` tokens over all live sequences (0 = 4096 per slot);
      * precision 0 = bf16 tensor-core products with f32 accumulation, 1 = every product in plain f32.  Their steps hold up to
@@ -117,6 +118,7 @@ typedef struct {
 #define B200RWKV_ARCH_KEMIRAX 100     /* b200rwkv_info.version of that family (num_head / head_size are per layer there: 0) */
 #define B200RWKV_ARCH_DEGAVIK 101
 #define B200RWKV_ARCH_ZUFULIX 102
+#define B200RWKV_ARCH_PASOPEL 103
 #define B200RWKV_QUANT_NONE 0
 #define B200RWKV_QUANT_INT8 1         /* blocks of 128 inputs: f16 (min, max) + 8-bit codes */
 #define B200RWKV_QUANT_NF4 2          /* blocks of 64 inputs: f16 absmax + 4-bit NormalFloat codes */
