@@ -280,6 +280,9 @@ struct KxLayer {
     float *sink = nullptr, *o_b = nullptr, *pcache = nullptr;
     int prow = 0;                                                // block-mean rows per page
     int sa_hb = 1, sa_gt = 1, sa_gt_decode = 1, sa_nbuf = 2, sa_nbuf_decode = 2;
+    int sa_qb = 1;                                               // tokens per chunk of the tile form in prompt steps
+    int sa_hb_decode = 1;                                        // query heads per CTA in decode-shaped steps
+    bool sa_reg = false;                                         // head sizes fit the register form of the attention kernel
     // per-sequence memory of fixed size, in the order of the flat state record
     struct Block { float* base; size_t per_slot; };
     std::vector<Block> fixed;
@@ -323,7 +326,7 @@ struct SeqModel {
     float* lin_ws = nullptr; size_t lin_ws_floats = 0;
     float* dbg_layers = nullptr;                  // [L][maxT][W] residual after every layer (bring-up aid; nullptr: off)
     int max_split = 16;
-    int sa_ygroups = 1;                           // head groups (grid rows) of the smallest windowed-attention launch of the model
+    int sa_ygroups = 1, sa_ygroups_decode = 1;    // head groups (grid rows) of the smallest windowed-attention launch of the model (prompt / decode shape)
     SeqMeta sm{nullptr, 0};
     size_t flat_floats(int ctx_rows) const;
     int max_D = 0;

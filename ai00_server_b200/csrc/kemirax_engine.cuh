@@ -498,7 +498,7 @@ void b200rwkv_engine::kx_fill_step(int* hm, const std::vector<int>& slots, const
         }
         const int tiles = cdiv(seen, WA_KT);
         ns = 1;
-        const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt) / std::max(1, m.sa_ygroups);   // CTAs the GPU holds at once
+        const int room = num_sms * (dec ? m.wa_ctas_decode : m.wa_ctas_prompt) / std::max(1, dec ? m.sa_ygroups_decode : m.sa_ygroups);   // CTAs the GPU holds at once
         const int* cap = dec ? m.cl_cap_decode : m.cl_cap_prompt;
         auto lg2 = [](int v) { int l = 0; while ((1 << l) < v) ++l; return l; };
         while (ns < m.max_split && std::max(1, nch) * ns * 2 <= room && std::max(1, nch) <= cap[lg2(ns * 2)] && tiles / (ns * 2) >= 1)

@@ -30,21 +30,40 @@ static inline int ps_heads_per_cta(int H, int G, int want) {
     return rep * (want / rep);
 }
 
+// the register form is built for key rows of one 512-byte piece per head.  (With three and five pieces, which the kernel's
+// template allows, a decode step of a 576-float latent row took 120 us where the tile form takes 84: every piece's loads wait
+// for the registers of the piece before it.)
+static inline SinkAttnKernel ps_attn_reg_kernel(int rb) {
+    return rb >= 4 ? sink_attn_reg_kernel<4, 1> : (rb == 2 ? sink_attn_reg_kernel<2, 1> : sink_attn_reg_kernel<1, 1>);
+}
+
 // how one attention launch of a layer runs: which kernel, its block size and shared memory, and the tile parameters
-struct PsAttnPlan { SinkAttnKernel kern; int threads; size_t smem; int gt, nbuf; };
+struct PsAttnPlan { SinkAttnKernel kern; int threads; size_t smem; int gt, nbuf, qb, ks, hb; };
 
 static PsAttnPlan ps_attn_plan(const KxLayer& l, int qb_prompt, bool decode) {
     const PsAttnShape a = ps_attn_shape(l.c);
-    const int qb = decode ? 1 : qb_prompt, rep = a.H / a.G, HB = l.sa_hb;
-    const int nhc = std::min(rep, HB), ncv = HB / nhc, rows = qb * nhc;      // rows of one key head in a full chunk
-    const int gt = decode ? l.sa_gt_decode : l.sa_gt, nbuf = decode ? l.sa_nbuf_decode : l.sa_nbuf;
-    int rb = SA_RB;
-    while (rb > 1 && std::min(gt, ncv) * cdiv(rows, rb) < 8) rb >>= 1;       // as many rows per warp as still leave 8 warps an item
+    const int rep = a.H / a.G, HB = decode ? l.sa_hb_decode : l.sa_hb;
+    const int nhc = std::min(rep, HB), ncv = HB / nhc;
     PsAttnPlan p;
+    p.hb = HB;
+    if (l.sa_reg) {
+        const int qb = decode ? 1 : qb_prompt, rows = qb * nhc;              // rows of one key head in a full chunk
+        const int rb = rows >= 4 ? 4 : (rows >= 2 ? 2 : 1);
+        const int items = ncv * cdiv(rows, rb);
+        int ks = 1;                                // few items (decode): the 8 warps share each item's key tiles
+        while (ks < 8 && items * ks * 2 <= SAR_THREADS / 32) ks *= 2;
+        p.kern = ps_attn_reg_kernel(rb); p.threads = SAR_THREADS; p.smem = sink_attn_reg_smem(qb, HB, rep, a.dv, rb, ks);
+        p.gt = 1; p.nbuf = 1; p.qb = qb; p.ks = ks;
+        return p;
+    }
+    const int qb = decode ? 1 : l.sa_qb, rows = qb * nhc;
+    const int gt = decode ? l.sa_gt_decode : l.sa_gt, nbuf = decode ? l.sa_nbuf_decode : l.sa_nbuf;
+    int rb = SA_RB;                                // as many rows per warp as still leave 8 warps an item (16 in decode-shaped
+    while (rb > 1 && std::min(gt, ncv) * cdiv(rows, rb) < (decode ? 16 : 8)) rb >>= 1;    // steps, whose CTAs have an SM to themselves)
     p.kern = ps_attn_kernel(rb);
     p.threads = std::min(gt, ncv) * cdiv(rows, rb) >= 16 ? SA_THREADS : 256;
     p.smem = sink_attn_smem(qb, HB, a.dk, a.dv, gt, nbuf, a.valias);
-    p.gt = gt; p.nbuf = nbuf;
+    p.gt = gt; p.nbuf = nbuf; p.qb = qb; p.ks = 1;
     return p;
 }
 
@@ -143,7 +162,7 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
     }
     // ---- the layer runs: the tensors of their layer, sequence memory of their own ----
     m.layers.resize(nr);
-    int qb = 4;
+    const int qb = 4;                              // tokens per chunk of a prompt step; a layer whose rows do not fit takes a part of a chunk per CTA
     for (int r = 0; r < nr; ++r) {
         KxLayer& l = m.layers[r];
         l = own[m.cfg.layers[r].tensors_of];
@@ -177,9 +196,13 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
         }
         // launch shape of the attention kernel: about 16 query heads per CTA, fewer (and then shorter chunks) where the rows of a
         // chunk would not fit into shared memory beside one tile
+        // the register form takes key / value sizes that are multiples of four up to 128; longer rows (a latent) and odd sizes
+        // go through shared-memory tiles
+        l.sa_reg = a.dk % 4 == 0 && a.dv % 4 == 0 && l.cache_D % 4 == 0 && a.dk <= 128 && a.dv <= 128;
         l.sa_hb = ps_heads_per_cta(a.H, a.G, 16);
-        while (sink_attn_smem(qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) > 160 * 1024) {
-            if (qb > 1) qb /= 2;
+        l.sa_qb = qb;
+        while (!l.sa_reg && sink_attn_smem(l.sa_qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) > 160 * 1024) {
+            if (l.sa_qb > 1) l.sa_qb /= 2;
             else {
                 REQUIRE(l.sa_hb > 1 && ps_heads_per_cta(a.H, a.G, l.sa_hb - 1) < l.sa_hb, B200RWKV_ERR_UNSUPPORTED,
                         "attention heads too large for shared memory");
@@ -188,13 +211,17 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
         }
     }
     m.qb_prompt = qb;
-    m.sa_ygroups = 1 << 30;
+    m.sa_ygroups = m.sa_ygroups_decode = 1 << 30;
     for (KxLayer& l : m.layers) {                  // as many key heads per tile load, and two tile buffers, where they fit
         const PsAttnShape a = ps_attn_shape(l.c);
         const int ncv = std::max(1, l.sa_hb / std::max(1, a.H / a.G));
+        // decode-shaped steps have one row per head: the register form then takes one key head per CTA, so that a chunk's tiles
+        // are spread over more warps
+        l.sa_hb_decode = l.sa_reg ? ps_heads_per_cta(a.H, a.G, std::max(1, a.H / a.G)) : l.sa_hb;
         m.sa_ygroups = std::min(m.sa_ygroups, cdiv(a.H, l.sa_hb));
+        m.sa_ygroups_decode = std::min(m.sa_ygroups_decode, cdiv(a.H, l.sa_hb_decode));
         for (int dec = 0; dec < 2; ++dec) {
-            const int q = dec ? 1 : qb;
+            const int q = dec ? 1 : l.sa_qb;
             int nbuf = 2, gt = ncv;
             if (sink_attn_smem(q, l.sa_hb, a.dk, a.dv, 1, 2, a.valias) > 200 * 1024) nbuf = 1;
             while (gt > 1 && sink_attn_smem(q, l.sa_hb, a.dk, a.dv, gt, nbuf, a.valias) > (dec ? 160 : 112) * 1024) gt = (gt + 1) / 2;
@@ -202,7 +229,10 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
             (dec ? l.sa_nbuf_decode : l.sa_nbuf) = nbuf;
         }
     }
-    for (int rb = 1; rb <= SA_RB; rb *= 2) CK(cudaFuncSetAttribute(ps_attn_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    for (int rb = 1; rb <= SA_RB; rb *= 2) {
+        CK(cudaFuncSetAttribute(ps_attn_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        CK(cudaFuncSetAttribute(ps_attn_reg_kernel(rb), cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    }
     // the largest cluster the attention launch may ask for: what the device can co-schedule at this layer's shared memory
     m.max_split = 8;
     m.wa_ctas_prompt = m.wa_ctas_decode = 8;
@@ -239,7 +269,8 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
         m.wa_ctas_decode = std::max(1, std::min(m.wa_ctas_decode, nd));
     }
     REQUIRE((size_t)W * 4 <= 200 * 1024, B200RWKV_ERR_UNSUPPORTED, "width too large for the norm kernel");
-    CK(cudaFuncSetAttribute(pre_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    CK(cudaFuncSetAttribute(pre_norm_kernel<NORM_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    CK(cudaFuncSetAttribute(pre_norm_kernel<PRE_NORM_THREADS_FEW_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 }
 
 // block means of a sequence's first n tokens, rebuilt from its cache rows (after a state import)
@@ -270,11 +301,11 @@ void b200rwkv_engine::ps_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
     Pending pend;
     auto boundary = [&](float* snap, const __nv_bfloat16* table, const float* vec, const float* weight, float* h, int compact, float* hidden) {
         PreNormParams pn{m.x, pend.rows, m.row_of, m.wgt, pend.top, pend.shared, snap, table, vec, weight, m.cfg.eps, h, compact, hidden, W, mv};
-        launch_k(pre_norm_kernel, dim3(rows), dim3(NORM_THREADS), (size_t)W * 4, pn, KC_LN, s, prof);
+        if (rows <= 32) launch_k(pre_norm_kernel<PRE_NORM_THREADS_FEW_ROWS>, dim3(rows), dim3(PRE_NORM_THREADS_FEW_ROWS), (size_t)W * 4, pn, KC_LN, s, prof);
+        else launch_k(pre_norm_kernel<NORM_THREADS>, dim3(rows), dim3(NORM_THREADS), (size_t)W * 4, pn, KC_LN, s, prof);
         pend = Pending();
     };
-    const int qb = decode ? 1 : m.qb_prompt;
-    const int chunks_grid = decode ? rows : cdiv(rows, qb) + nslot_grid;
+    const int chunks_grid = decode ? rows : cdiv(rows, m.qb_prompt) + nslot_grid;
     for (size_t li = 0; li < m.layers.size(); ++li) {
         KxLayer& l = m.layers[li];
         const KxLayerCfg& c = l.c;
@@ -287,8 +318,11 @@ void b200rwkv_engine::ps_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
         SinkAttnParams sp;
         memset(&sp, 0, sizeof(sp));
         sp.cache = l.cache; sp.table = m.d_table; sp.stride = m.npages; sp.page = m.page; sp.D = l.cache_D;
-        sp.sink = l.sink; sp.H = a.H; sp.G = a.G; sp.dk = a.dk; sp.dv = a.dv; sp.HB = l.sa_hb; sp.win = c.window;
-        sp.qb = qb; sp.gt = plan.gt; sp.cl = nsplit; sp.nbuf = plan.nbuf; sp.valias = a.valias ? 1 : 0; sp.meta = mv; sp.sm = m.sm;
+        sp.sink = l.sink; sp.H = a.H; sp.G = a.G; sp.dk = a.dk; sp.dv = a.dv; sp.HB = plan.hb; sp.win = c.window;
+        sp.qb = plan.qb; sp.gt = plan.gt; sp.cl = nsplit; sp.nbuf = plan.nbuf; sp.valias = a.valias ? 1 : 0; sp.ks = plan.ks;
+        sp.nsub = decode ? 1 : m.qb_prompt / plan.qb;
+        sp.meta = mv; sp.sm = m.sm;
+        const dim3 attn_grid(chunks_grid * sp.nsub * nsplit, cdiv(a.H, plan.hb));
         if (c.mixer == KX_SINK) {
             const int G_ = c.kv_heads, dk = c.dim, C_ = l.conv_C;
             ShortConvParams cp{m.pr, PN, m.cv, C_, l.conv_w, l.conv_tail, C_, c.taps, mv, 0};
@@ -300,12 +334,12 @@ void b200rwkv_engine::ps_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
             launch_k(bias_attn_prep_kernel, dim3(rows), dim3(128), 0, ap, KC_OTHER, s, prof);
             if (c.pool > 0) {
                 PoolWriteParams pw{l.cache, l.pcache, m.d_table, m.npages, m.page, l.cache_D, c.pool, l.prow, 0, 0, mv, m.sm};
-                launch_k(pool_write_kernel, dim3(rows), dim3(128), 0, pw, KC_OTHER, s, prof);
+                launch_k(pool_write_kernel, dim3(rows, cdiv(l.cache_D, 128)), dim3(128), 0, pw, KC_OTHER, s, prof);
             }
             sp.q = m.q; sp.ldq = H_ * dk; sp.pcache = l.pcache; sp.koff = 0; sp.voff = G_ * dk; sp.out = m.vout; sp.ldo = H_ * dv;
             sp.gate = m.pr + C_; sp.ldg = PN; sp.scale = 1.f; sp.pool = c.pool; sp.prow = l.prow;
             launch_cluster = nsplit;
-            launch_k(plan.kern, dim3(chunks_grid * nsplit, cdiv(a.H, l.sa_hb)), dim3(plan.threads), plan.smem, sp, KC_WKV, s, prof);
+            launch_k(plan.kern, attn_grid, dim3(plan.threads), plan.smem, sp, KC_WKV, s, prof);
         } else {
             const int dn = c.dim, dr = c.rot_dim, rk = c.kv_rank, D = rk + dr, QW = H_ * (dn + dr);
             RmsRowsParams rr{m.pr, PN, m.cq, c.q_rank, l.dq_norm, c.q_rank, 1, m.cfg.eps, cntT};
@@ -323,7 +357,7 @@ void b200rwkv_engine::ps_enqueue_layers(cudaStream_t s, int rows, int nslot_grid
             launch_k(kv_write_kernel, dim3(rows), dim3(128), 0, kw, KC_OTHER, s, prof);
             sp.q = m.qa; sp.ldq = H_ * D; sp.out = m.olat; sp.ldo = H_ * rk; sp.scale = c.scale;
             launch_cluster = nsplit;
-            launch_k(plan.kern, dim3(chunks_grid * nsplit, cdiv(a.H, l.sa_hb)), dim3(plan.threads), plan.smem, sp, KC_WKV, s, prof);
+            launch_k(plan.kern, attn_grid, dim3(plan.threads), plan.smem, sp, KC_WKV, s, prof);
             {   // values of every head from its weighted latent, through the output gate
                 LinParams p = lin(m.olat, H_ * rk, l.uv, m.vout, H_ * dv, dv, rk, LE_MUL_SIGMOID);
                 p.x_gstride = rk; p.w_gstride = (long long)dv * rk; p.y_gstride = dv;

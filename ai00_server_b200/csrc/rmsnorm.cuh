@@ -223,7 +223,10 @@ struct PreNormParams {
     MetaView meta;
 };
 
-__global__ void __launch_bounds__(NORM_THREADS) pre_norm_kernel(const PreNormParams p) {
+constexpr int PRE_NORM_THREADS_FEW_ROWS = 1024;    // block size for steps of few tokens (decode): a thread then owns one or two columns
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS) pre_norm_kernel(const PreNormParams p) {
     __shared__ float red[32];
     extern __shared__ __align__(16) float pre_norm_row[];      // [W]
     const int t = blockIdx.x;

@@ -496,6 +496,99 @@ def zufulix_main(args):
         print(json.dumps(_degavik_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
 
 
+PS_SIZES = {
+    # width; attention layers: heads / key heads / head size, window, tokens per block mean, convolution taps; latent layers: heads, plain /
+    # rotated / value sizes, ranks, window; experts x ff, top, shared ff; dense ff; vocab.  Width, depth, head counts, head sizes and
+    # vocabulary are those of ZF_SIZES, the latent sizes those of KX_SIZES; the experts are gated units (three matrices), the dense
+    # feed-forward has two, so their hidden sizes are DG_SIZES' and ZF_SIZES' for the same number of weights
+    "w1024": dict(width=1024, heads=8, kv_heads=2, dim=128, window=512, pool=16, conv=4, rot_dim=64, vdim=128, kv_rank=256, q_rank=384,
+                  experts=8, ff=512, top=2, shared_ff=1024, dense_ff=4224, vocab=32768),
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, window=512, pool=16, conv=4, rot_dim=64, vdim=128, kv_rank=512, q_rank=768,
+                  experts=16, ff=1024, top=4, shared_ff=2048, dense_ff=8448, vocab=32768),
+}
+
+
+def _zufulix_arm(args, name, time_arm, hbm, tf, peak_kind):
+    """One JSON record: the four-layer Zufulix stack (attention over the whole context with a distance bias: dense, experts, experts,
+    dense feed-forwards; four residual streams)."""
+    from ai00_server_b200 import runtime, synth
+    B, ctx = args.batch, args.context
+    L = synth.zufulix_layer
+    z = ZF_SIZES[name]
+    W, V, H, G, dk, dv, E, top = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["experts"], z["top"]
+    att = dict(heads=H, kv_heads=G, dim=dk, vdim=dv, bias_max=z["bias_max"])
+    moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], groups=z["groups"])
+    dense = dict(mlp="dense", ff=z["dense_ff"])
+    layers = [L(**att, **dense), L(**att, **moe), L(**att, **moe), L(**att, **dense)]
+    cfg, st, _ = synth.make_zufulix(layers, width=W, vocab=V, seed=1, streams=z["streams"], rel_rows=z["rel_rows"], arrays=False)
+    mix = H * dk * W + G * dk * W + G * dv * W + W * H * dv
+    ff_moe, ff_dense, expert = E * W, 2 * W * z["dense_ff"], 2 * W * z["ff"]
+    per_layer = [mix + ff_dense, mix + ff_moe, mix + ff_moe, mix + ff_dense]
+    reach = min(E, B * top)
+    active = sum(per_layer) + 2 * top * expert + V * W
+    step_bytes = 2 * (sum(per_layer) + 2 * reach * expert + V * W) + 4 * B * ctx * G * (dk + dv) * 4
+    attn_flops_tok = 4 * 2 * H * (dk + dv) * ctx / 2
+    m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+    r = time_arm(m, V, m.state.reset)
+    m.close()
+    r.update({"family": "zufulix", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+              "decode_algorithmic_bytes_per_step": int(step_bytes),
+              "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+              "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+              "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+              "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+    return r
+
+
+def pasopel_main(args):
+    """Prefill and decode throughput of the Pasopel family (windowed attention with block means + dense, windowed latent attention +
+    experts twice, windowed attention + experts; the two latent layers form a loop that runs once) beside the closest existing
+    family, a Zufulix stack of equal width, depth, head counts, head sizes and vocabulary."""
+    from ai00_server_b200 import runtime, synth
+    peaks, peak_kind = read_peaks()
+    hbm, tf = float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0))
+    B, ctx = args.batch, args.context
+    time_arm = _family_timer(args, np.random.default_rng(7))
+    L = synth.pasopel_layer
+    for name in args.kx_sizes.split(","):
+        z = PS_SIZES[name]
+        W, V, H, G, dk, E, top = z["width"], z["vocab"], z["heads"], z["kv_heads"], z["dim"], z["experts"], z["top"]
+        dr, dv, rk, rq, win, pool = z["rot_dim"], z["vdim"], z["kv_rank"], z["q_rank"], z["window"], z["pool"]
+        att = dict(heads=H, kv_heads=G, dim=dk, window=win, pool=pool, conv=z["conv"])
+        lat = dict(heads=H, dim=dk, rot_dim=dr, vdim=dv, kv_rank=rk, q_rank=rq, window=win, base=5e5)
+        moe = dict(mlp="moe", experts=E, top=top, ff=z["ff"], shared_ff=z["shared_ff"])
+        dense = dict(mlp="dense", ff=z["dense_ff"])
+        layers = [L("attention", **att, **dense), L("latent_attention", **lat, **moe), L("latent_attention", **lat, **moe), L("attention", **att, **moe)]
+        cfg, st, _ = synth.make_pasopel(layers, width=W, vocab=V, seed=1, loop=(1, 3, 1), softcap=30.0, arrays=False)
+        # algorithmic work: weights one token touches, weights a decode step streams (dense + reachable experts; the embedding
+        # table is the output matrix), cache rows inside the windows and one block-mean row per `pool` older tokens
+        mix_a = H * dk * W + G * dk * W + H * dk * W + W * H * dk
+        mix_l = rq * W + H * (dk + dr) * rq + (rk + dr) * W + H * dk * rk + H * dv * rk + H * dv * W + W * H * dv
+        ff_moe, ff_dense, expert = E * W + 3 * W * z["shared_ff"], 2 * W * z["dense_ff"], 3 * W * z["ff"]
+        per_layer = [mix_a + ff_dense, mix_l + ff_moe, mix_l + ff_moe, mix_a + ff_moe]
+        reach = min(E, B * top)
+        active = sum(per_layer) + 3 * top * expert + V * W
+        seen_a = min(ctx, win) + max(0, ctx - win) // pool
+        cache_bytes = 2 * B * seen_a * G * 2 * dk * 4 + 2 * B * min(ctx, win) * (rk + dr) * 4
+        step_bytes = 2 * (sum(per_layer) + 3 * reach * expert + V * W) + cache_bytes
+        # scores + values during the prompt: the window fills over the first `win` tokens, the latent layers score and sum the shared
+        # row (absorbed form)
+        mean_seen = (min(ctx, win) ** 2 / 2 + max(0, ctx - win) * win) / ctx
+        attn_flops_tok = 2 * 2 * H * 2 * dk * (mean_seen + max(0, ctx - win) / 2 / pool) + 2 * 2 * H * (2 * rk + dr) * mean_seen
+        m = runtime.Model(st, max_batch=B, token_chunk_size=512, config=cfg, kv_tokens=B * (ctx + args.warmup + args.steps + 8))
+        r = time_arm(m, V, m.state.reset)
+        m.close()
+        r.update({"family": "pasopel", "size": name, "batch": B, "context": ctx, "params_active_per_token": int(active),
+                  "decode_algorithmic_bytes_per_step": int(step_bytes),
+                  "decode_frac_of_hbm_peak": step_bytes / (r["decode_ms_per_step"] * 1e-3) / (hbm * 1e9),
+                  "prefill_tflops": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12,
+                  "prefill_frac_of_bf16_peak": (2 * active + attn_flops_tok) * r["prefill_tokens_per_s"] / 1e12 / tf,
+                  "peaks": peak_kind, "dtype": "bf16", "data": "synthetic"})
+        print(json.dumps(r), flush=True)
+        del st
+        print(json.dumps(_zufulix_arm(args, name, time_arm, hbm, tf, peak_kind)), flush=True)
+
+
 def main():
     global PRESET, BATCH
     ap = argparse.ArgumentParser()
@@ -514,10 +607,10 @@ def main():
     ap.add_argument("--quant-layers", type=int, default=-1, help="the reference's `quant`: first N layers (default: all)")
     ap.add_argument("--seqs", type=int, default=256)
     ap.add_argument("--seq-len", type=int, default=512)
-    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax", "degavik", "zufulix"],
-                    help="kemirax / degavik / zufulix: prefill and decode throughput of that family at layer sizes of a real model (random "
+    ap.add_argument("--family", default="rwkv", choices=["rwkv", "kemirax", "degavik", "zufulix", "pasopel"],
+                    help="kemirax / degavik / zufulix / pasopel: prefill and decode throughput of that family at layer sizes of a real model (random "
                          "weights), beside the closest existing family at equal width and depth (RWKV-7 for kemirax, Kemirax for degavik, "
-                         "Degavik for zufulix); one "
+                         "Degavik for zufulix, Zufulix for pasopel); one "
                          "JSON line per arm (not the headline workload)")
     ap.add_argument("--kx-sizes", default="w1024,w2048", help="--family kemirax / degavik / zufulix: comma-separated size names")
     ap.add_argument("--context", type=int, default=1024,
@@ -530,6 +623,8 @@ def main():
         return degavik_main(args)
     if args.family == "zufulix":
         return zufulix_main(args)
+    if args.family == "pasopel":
+        return pasopel_main(args)
     PRESET, BATCH = args.preset, args.batch
     METRIC = metric_name(PRESET, BATCH)
     if args.quant != "none":
