@@ -638,7 +638,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     from ai00_server_b200 import synth
-    from oracle import rwkv_numpy as O          # only for parse_st of the cpu arm (checker side)
+    from oracle import rwkv_numpy as O          # only for parse_st of the cpu arm (oracle side)
     shape = synth.PRESETS[PRESET]
     config = {"workload": f"{PRESET} decode, batch {BATCH} slots x 1 token/step, {PROMPT}-token synthetic prompt per slot",
               "preset": PRESET, "batch": BATCH, "prompt_tokens": PROMPT, "parallelism": f"tp{world}",
