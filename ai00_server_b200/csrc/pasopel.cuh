@@ -34,7 +34,8 @@ static KxConfig ps_parse_config(const JVal& root) {
         REQUIRE(l.kind == JVal::OBJ && l.has("type") && l.at("type").kind == JVal::STR, B200RWKV_ERR_INVALID, "config: layer without a type");
         const std::string type = l.at("type").str;
         const JVal& m = l.at("mixer");
-        k.heads = m.integer("heads"); k.dim = m.integer("dim"); k.vdim = m.integer("vdim");
+        k.heads = m.integer("heads"); k.dim = m.integer("dim");
+        k.vdim = m.has("vdim") ? m.integer("vdim") : k.dim;
         k.scale = (float)m.number("scale");
         const JVal& mk = m.at("mask");
         k.window = mk.integer("size");

@@ -58,8 +58,10 @@ static PsAttnPlan ps_attn_plan(const KxLayer& l, int qb_prompt, bool decode) {
     }
     const int qb = decode ? 1 : l.sa_qb, rows = qb * nhc;
     const int gt = decode ? l.sa_gt_decode : l.sa_gt, nbuf = decode ? l.sa_nbuf_decode : l.sa_nbuf;
-    int rb = SA_RB;                                // as many rows per warp as still leave 8 warps an item (16 in decode-shaped
-    while (rb > 1 && std::min(gt, ncv) * cdiv(rows, rb) < (decode ? 16 : 8)) rb >>= 1;    // steps, whose CTAs have an SM to themselves)
+    // rows per warp: every key float a lane reads from the tile feeds one product per row, and the tile loop is bound by
+    // shared-memory reads, so as many rows as still leave 4 warps an item (8 in decode-shaped
+    int rb = SA_RB;
+    while (rb > 1 && std::min(gt, ncv) * cdiv(rows, rb) < (decode ? 8 : 4)) rb >>= 1;    // steps, whose CTAs have an SM to themselves)
     p.kern = ps_attn_kernel(rb);
     p.threads = std::min(gt, ncv) * cdiv(rows, rb) >= 16 ? SA_THREADS : 256;
     p.smem = sink_attn_smem(qb, HB, a.dk, a.dv, gt, nbuf, a.valias);
@@ -201,20 +203,26 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
         l.sa_reg = a.dk % 4 == 0 && a.dv % 4 == 0 && l.cache_D % 4 == 0 && a.dk <= 128 && a.dv <= 128;
         l.sa_hb = ps_heads_per_cta(a.H, a.G, 16);
         l.sa_qb = qb;
-        while (!l.sa_reg && sink_attn_smem(l.sa_qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) > 160 * 1024) {
-            if (l.sa_qb > 1) l.sa_qb /= 2;
-            else {
-                REQUIRE(l.sa_hb > 1 && ps_heads_per_cta(a.H, a.G, l.sa_hb - 1) < l.sa_hb, B200RWKV_ERR_UNSUPPORTED,
-                        "attention heads too large for shared memory");
-                l.sa_hb = ps_heads_per_cta(a.H, a.G, l.sa_hb - 1);
+        // tile form: rows (tokens x heads) per CTA such that two CTAs fit an SM beside one tile each (one loads while the other
+        // multiplies); where that would leave fewer than four rows, one CTA per SM
+        const int hb0 = l.sa_hb;
+        for (size_t target : {(size_t)112 * 1024, (size_t)160 * 1024}) {
+            if (l.sa_reg) break;
+            l.sa_qb = qb; l.sa_hb = hb0;
+            while (sink_attn_smem(l.sa_qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) > target) {
+                if (l.sa_qb > 1) l.sa_qb /= 2;
+                else if (l.sa_hb > 1 && ps_heads_per_cta(a.H, a.G, l.sa_hb / 2) < l.sa_hb) l.sa_hb = ps_heads_per_cta(a.H, a.G, l.sa_hb / 2);
+                else break;
             }
+            if (sink_attn_smem(l.sa_qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) <= target && l.sa_qb * l.sa_hb >= 4) break;
         }
+        REQUIRE(l.sa_reg || sink_attn_smem(l.sa_qb, l.sa_hb, a.dk, a.dv, 1, 1, a.valias) <= 160 * 1024, B200RWKV_ERR_UNSUPPORTED,
+                "attention heads too large for shared memory");
     }
     m.qb_prompt = qb;
     m.sa_ygroups = m.sa_ygroups_decode = 1 << 30;
     for (KxLayer& l : m.layers) {                  // as many key heads per tile load, and two tile buffers, where they fit
         const PsAttnShape a = ps_attn_shape(l.c);
-        const int ncv = std::max(1, l.sa_hb / std::max(1, a.H / a.G));
         // decode-shaped steps have one row per head: the register form then takes one key head per CTA, so that a chunk's tiles
         // are spread over more warps
         l.sa_hb_decode = l.sa_reg ? ps_heads_per_cta(a.H, a.G, std::max(1, a.H / a.G)) : l.sa_hb;
@@ -222,9 +230,10 @@ void b200rwkv_engine::ps_load(const StFile& st, KxSizes& z) {
         m.sa_ygroups_decode = std::min(m.sa_ygroups_decode, cdiv(a.H, l.sa_hb_decode));
         for (int dec = 0; dec < 2; ++dec) {
             const int q = dec ? 1 : l.sa_qb;
+            const int hb = dec ? l.sa_hb_decode : l.sa_hb, ncv = std::max(1, hb / std::max(1, a.H / a.G));
             int nbuf = 2, gt = ncv;
-            if (sink_attn_smem(q, l.sa_hb, a.dk, a.dv, 1, 2, a.valias) > 200 * 1024) nbuf = 1;
-            while (gt > 1 && sink_attn_smem(q, l.sa_hb, a.dk, a.dv, gt, nbuf, a.valias) > (dec ? 160 : 112) * 1024) gt = (gt + 1) / 2;
+            if (sink_attn_smem(q, hb, a.dk, a.dv, 1, 2, a.valias) > (size_t)(dec ? 200 : 112) * 1024) nbuf = 1;
+            while (gt > 1 && sink_attn_smem(q, hb, a.dk, a.dv, gt, nbuf, a.valias) > (dec ? 160 : 112) * 1024) gt = (gt + 1) / 2;
             (dec ? l.sa_gt_decode : l.sa_gt) = gt;
             (dec ? l.sa_nbuf_decode : l.sa_nbuf) = nbuf;
         }

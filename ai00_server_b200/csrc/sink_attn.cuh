@@ -275,6 +275,39 @@ __global__ void __launch_bounds__(SA_THREADS) sink_attn_kernel(const SinkAttnPar
                 __syncwarp();
                 // ---- weights x values ----
                 const float* vt = cV + (size_t)cl_ * SA_KT * tsv;
+                if (vec) {                         // four neighbouring outputs per lane: a 16-byte value load feeds 4 RB products
+                    for (int d = lane * 4; d < dv; d += 128) {
+                        float4 acc[RBT];
+#pragma unroll
+                        for (int b = 0; b < RBT; ++b) {
+                            const float f = sScl[rows[b]];
+                            acc[b] = *reinterpret_cast<const float4*>(sO + (size_t)rows[b] * dv + d);
+                            acc[b].x *= f; acc[b].y *= f; acc[b].z *= f; acc[b].w *= f;
+                        }
+#pragma unroll 2
+                        for (int kt = 0; kt < SA_KT; kt += 4) {
+                            const float4 v0 = *reinterpret_cast<const float4*>(vt + (kt + 0) * tsv + d);
+                            const float4 v1 = *reinterpret_cast<const float4*>(vt + (kt + 1) * tsv + d);
+                            const float4 v2 = *reinterpret_cast<const float4*>(vt + (kt + 2) * tsv + d);
+                            const float4 v3 = *reinterpret_cast<const float4*>(vt + (kt + 3) * tsv + d);
+#pragma unroll
+                            for (int b = 0; b < RBT; ++b) {
+                                const float4 w4 = *reinterpret_cast<const float4*>(sP + rows[b] * SA_KT + kt);
+                                acc[b].x = fmaf(w4.x, v0.x, acc[b].x); acc[b].y = fmaf(w4.x, v0.y, acc[b].y);
+                                acc[b].z = fmaf(w4.x, v0.z, acc[b].z); acc[b].w = fmaf(w4.x, v0.w, acc[b].w);
+                                acc[b].x = fmaf(w4.y, v1.x, acc[b].x); acc[b].y = fmaf(w4.y, v1.y, acc[b].y);
+                                acc[b].z = fmaf(w4.y, v1.z, acc[b].z); acc[b].w = fmaf(w4.y, v1.w, acc[b].w);
+                                acc[b].x = fmaf(w4.z, v2.x, acc[b].x); acc[b].y = fmaf(w4.z, v2.y, acc[b].y);
+                                acc[b].z = fmaf(w4.z, v2.z, acc[b].z); acc[b].w = fmaf(w4.z, v2.w, acc[b].w);
+                                acc[b].x = fmaf(w4.w, v3.x, acc[b].x); acc[b].y = fmaf(w4.w, v3.y, acc[b].y);
+                                acc[b].z = fmaf(w4.w, v3.z, acc[b].z); acc[b].w = fmaf(w4.w, v3.w, acc[b].w);
+                            }
+                        }
+#pragma unroll
+                        for (int b = 0; b < RBT; ++b)
+                            if (b < nr) *reinterpret_cast<float4*>(sO + (size_t)rows[b] * dv + d) = acc[b];
+                    }
+                } else
                 for (int d = lane; d < dv; d += 32) {
                     float acc[RBT];
 #pragma unroll
